@@ -135,7 +135,15 @@ typedef struct {
     uint64_t peak_bytes_in_use;
 } mk_alloc_stats_t;
 
-/* Creates a lazy buffer: no device memory is reserved until the first mk_buf_ptr /
+/* Reuse is stream-ordered.  The reference issues every CUDA call on one stream and leaves ordering to its
+ * scheduler (device/src/allocator.rs:72-112); here kernels run on several non-blocking streams, so a block
+ * that goes back to the cache remembers, for every stream of this device that had work enqueued through the
+ * library, an event behind that work, and the caller that takes the block out of the cache waits for those
+ * events first (usually they completed long ago).  mk_free therefore never needs a preceding sync -- as long
+ * as the work that uses the buffer was enqueued through this library (mk_launch included) before the free.
+ * MK_ALLOC_ZERO_INIT zeros are in place when the allocating call returns.
+ *
+ * Creates a lazy buffer: no device memory is reserved until the first mk_buf_ptr /
  * mk_buf_ensure / copy.  size may be 0. */
 MK_API mk_status mk_alloc(mk_device* dev, size_t bytes, uint32_t flags, mk_buf** out);
 /* Forces allocation (BufferData::ensure_allocated). */
@@ -177,6 +185,11 @@ MK_API mk_status mk_host_free(void* p);
  * 1 = D2H, 2 = D2D. */
 MK_API mk_status mk_memcpy_async(mk_device* dev, void* dst, const void* src, size_t bytes, int32_t kind,
                                  mk_stream* s);
+/* CudaAllocator::memset_zeros (device/src/allocator.rs:256-309) for any byte value: fills `bytes` bytes at
+ * the device pointer `dst` on stream s. */
+MK_API mk_status mk_memset_async(mk_device* dev, void* dst, int32_t byte_value, size_t bytes, mk_stream* s);
+/* Free and total device memory as the driver reports them (cudaMemGetInfo). */
+MK_API mk_status mk_mem_info(mk_device* dev, size_t* free_bytes, size_t* total_bytes);
 
 /* ---------------------------------------------------------------------------------------------
  * Module load and launch  (JitKernel compile+load+fn pointer: runtime/src/jit_loader.rs:31-38;
@@ -305,15 +318,25 @@ MK_API mk_status mk_tuning_clear(mk_device* dev);
  *                   of 8 elements (anything else: MK_ERR_UNSUPPORTED -- use mk_gemm), and
  *                   batch <= MK_STATIC_GEMM_MAX_BATCH (more: MK_ERR_INVALID, nothing is launched)
  *   kernel_error    NULL, or where to store the kernel error word: when given, the call waits for the
- *                   stream and returns MK_ERR_KERNEL if a pipeline wait gave up
+ *                   stream and returns MK_ERR_KERNEL if a pipeline wait gave up (not allowed while the
+ *                   stream is capturing: MK_ERR_INVALID).  With NULL the call only enqueues; a wait that
+ *                   gave up then stays unreported until mk_gemm_static_status (or the next call with a
+ *                   pointer) reads the words.
  *
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and the
- * device's attributes; make that first call before any stream capture begins.
+ * device's attributes, and the first launch of each kernel variant makes the driver load that kernel's
+ * image; make that first call before any stream capture begins.  The calling thread's current device is
+ * left as it was.  Problems with more than 128 rows and enough 256 x 256 tiles run on the CTA-pair kernel,
+ * like mk_gemm.
  * All calls on a device share the array.  Each call clears, in stream order, the words it uses, so
  * calls queued on one stream are fine; calls that overlap on the GPU (different streams, different
  * host threads) race on the error words -- results in C stay correct, error reporting does not. */
 #define MK_STATIC_GEMM_MAX_BATCH 256
 MK_API mk_status mk_gemm_static(int32_t device_ordinal, void* cuda_stream, const mk_gemm_desc* desc, uint32_t* kernel_error);
+/* Waits for `cuda_stream` and reads the first `batch` error words of the static array (what the last
+ * mk_gemm_static call with that batch wrote): *kernel_error receives the first non-zero word and the call
+ * returns MK_ERR_KERNEL, or 0 and MK_OK.  Allocates nothing.  (No counterpart in the reference.) */
+MK_API mk_status mk_gemm_static_status(int32_t device_ordinal, void* cuda_stream, int32_t batch, uint32_t* kernel_error);
 
 /* ---------------------------------------------------------------------------------------------
  * Attention forward -- replaces the >= 5 kernels morok schedules for
@@ -407,9 +430,11 @@ MK_API mk_status mk_all_gather_push_2d(mk_device* dev, mk_stream* s, const void*
                                        size_t dst_offset, size_t dst_pitch);
 
 /* ---------------------------------------------------------------------------------------------
- * Kernel error word.  Kernels never trap or spin without bound: a pipeline wait that runs out
- * records a code here and the kernel returns.  mk_kernel_status reads and clears it after
- * synchronising the stream; non-zero yields MK_ERR_KERNEL.  Codes name the kernel and the waiting
+ * Kernel error words.  Kernels never trap or spin without bound: a pipeline wait that runs out
+ * records a code in the error word of the stream the kernel was launched on (every stream has its own
+ * word; a recorded plan has one too, whichever stream replays it) and the kernel returns.
+ * mk_kernel_status synchronises stream `s`, then reads and clears the word of `s` and the words of
+ * recorded plans; non-zero yields MK_ERR_KERNEL.  Words of other streams stay for their own queries.  Codes name the kernel and the waiting
  * role: 0x101-0x103 tensor-core GEMM (producer, MMA issuer, epilogue), 0x201-0x203 tensor-core
  * attention (producer, MMA issuer, softmax), 0x301-0x303 few-row GEMM (producer, consumer, reduction),
  * 0x901 the self-test below.

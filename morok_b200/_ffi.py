@@ -103,12 +103,15 @@ PROTOTYPES = {
     "mk_host_alloc": (i32, [sz, P(vp)]),
     "mk_host_free": (i32, [vp]),
     "mk_memcpy_async": (i32, [vp, vp, vp, sz, i32, vp]),
+    "mk_memset_async": (i32, [vp, vp, i32, sz, vp]),
+    "mk_mem_info": (i32, [vp, P(sz), P(sz)]),
     "mk_module_load": (i32, [vp, vp, sz, P(vp)]),
     "mk_module_unload": (i32, [vp]),
     "mk_get_function": (i32, [vp, C.c_char_p, P(vp)]),
     "mk_launch": (i32, [vp, P(u32), P(u32), u32, vp, P(vp)]),
     "mk_gemm": (i32, [vp, vp, P(GemmDesc)]),
     "mk_gemm_static": (i32, [i32, vp, P(GemmDesc), P(u32)]),
+    "mk_gemm_static_status": (i32, [i32, vp, i32, P(u32)]),
     "mk_gemm_autotune": (i32, [vp, vp, P(GemmDesc), i32, P(GemmTuning)]),
     "mk_gemm_tuning_set": (i32, [vp, P(GemmDesc), P(GemmTuning)]),
     "mk_gemm_tuning_get": (i32, [vp, P(GemmDesc), P(GemmTuning), P(i32)]),

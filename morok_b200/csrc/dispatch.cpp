@@ -5,30 +5,47 @@
 
 using namespace mk;
 
+namespace mk {
+// The descriptor rules every GEMM entry point shares (mk_gemm and mk_gemm_static): dtypes, dimensions,
+// leading dimensions, epilogue and flag combinations, peers.  Normalises batch <= 0 to 1.  *nothing_to_do is
+// set for M == 0 or N == 0 (no output elements), which skips the pointer checks.
+mk_status validate_gemm_desc(mk_gemm_desc& d, const char* who, bool* nothing_to_do) {
+    *nothing_to_do = false;
+    MK_REQUIRE((dtype_valid(d.dtype_in) || dtype_is_fp8(d.dtype_in)) && dtype_valid(d.dtype_out),
+               "%s: unsupported dtype (%d -> %d): inputs f32 / bf16 / f16 / 8-bit float, output f32 / bf16 / f16", who, d.dtype_in, d.dtype_out);
+    MK_REQUIRE(d.M >= 0 && d.N >= 0 && d.K >= 0, "%s: negative dimension (M=%lld N=%lld K=%lld)", who, (long long)d.M,
+               (long long)d.N, (long long)d.K);
+    if (d.batch <= 0) d.batch = 1;
+    if (d.M == 0 || d.N == 0) {
+        *nothing_to_do = true;
+        return MK_OK;
+    }
+    MK_REQUIRE(d.C, "%s: null C", who);
+    MK_REQUIRE(d.K == 0 || (d.A && d.B), "%s: null A or B", who);
+    MK_REQUIRE(d.lda >= d.K, "%s: lda %lld < K %lld", who, (long long)d.lda, (long long)d.K);
+    MK_REQUIRE(d.ldb >= (d.trans_b ? d.K : d.N), "%s: ldb %lld too small", who, (long long)d.ldb);
+    MK_REQUIRE(d.ldc >= d.N, "%s: ldc %lld < N %lld", who, (long long)d.ldc, (long long)d.N);
+    MK_REQUIRE(d.epilogue >= MK_EPI_NONE && d.epilogue <= MK_EPI_SWIGLU, "%s: unknown epilogue %d", who, d.epilogue);
+    MK_REQUIRE(d.epilogue == MK_EPI_NONE || d.epilogue == MK_EPI_SWIGLU || d.D, "%s: the epilogue needs D", who);
+    MK_REQUIRE(d.epilogue != MK_EPI_SWIGLU || (d.B2 && d.K > 0 && d.n_peers == 0 && !(d.flags & MK_GEMM_SCALED)),
+               "%s: MK_EPI_SWIGLU needs B2 and K > 0, and takes neither peers nor alpha / beta", who);
+    MK_REQUIRE((d.flags & ~(uint32_t)(MK_GEMM_SCALED | MK_GEMM_GATE_SIGMOID)) == 0, "%s: unknown flags 0x%x", who, d.flags);
+    MK_REQUIRE(!(d.flags & MK_GEMM_GATE_SIGMOID) || d.epilogue == MK_EPI_SWIGLU, "%s: MK_GEMM_GATE_SIGMOID belongs to MK_EPI_SWIGLU", who);
+    MK_REQUIRE(d.n_peers >= 0 && d.n_peers <= MK_MAX_PEERS, "%s: n_peers %d out of range", who, d.n_peers);
+    for (int i = 0; i < d.n_peers; ++i) MK_REQUIRE(d.peer_C[i], "%s: peer_C[%d] is null", who, i);
+    return MK_OK;
+}
+}  // namespace mk
+
 extern "C" {
 
 mk_status mk_gemm(mk_device* dev, mk_stream* s, const mk_gemm_desc* desc) {
     MK_REQUIRE(dev && desc, "mk_gemm: null argument");
     mk_gemm_desc d = *desc;
-    MK_REQUIRE((dtype_valid(d.dtype_in) || dtype_is_fp8(d.dtype_in)) && dtype_valid(d.dtype_out),
-               "mk_gemm: unsupported dtype (%d -> %d): inputs f32 / bf16 / f16 / 8-bit float, output f32 / bf16 / f16", d.dtype_in, d.dtype_out);
-    MK_REQUIRE(d.M >= 0 && d.N >= 0 && d.K >= 0, "mk_gemm: negative dimension (M=%lld N=%lld K=%lld)", (long long)d.M,
-               (long long)d.N, (long long)d.K);
-    if (d.batch <= 0) d.batch = 1;
-    if (d.M == 0 || d.N == 0) return MK_OK;
-    MK_REQUIRE(d.C, "mk_gemm: null C");
-    MK_REQUIRE(d.K == 0 || (d.A && d.B), "mk_gemm: null A or B");
-    MK_REQUIRE(d.lda >= d.K, "mk_gemm: lda %lld < K %lld", (long long)d.lda, (long long)d.K);
-    MK_REQUIRE(d.ldb >= (d.trans_b ? d.K : d.N), "mk_gemm: ldb %lld too small", (long long)d.ldb);
-    MK_REQUIRE(d.ldc >= d.N, "mk_gemm: ldc %lld < N %lld", (long long)d.ldc, (long long)d.N);
-    MK_REQUIRE(d.epilogue >= MK_EPI_NONE && d.epilogue <= MK_EPI_SWIGLU, "mk_gemm: unknown epilogue %d", d.epilogue);
-    MK_REQUIRE(d.epilogue == MK_EPI_NONE || d.epilogue == MK_EPI_SWIGLU || d.D, "mk_gemm: the epilogue needs D");
-    MK_REQUIRE(d.epilogue != MK_EPI_SWIGLU || (d.B2 && d.K > 0 && d.n_peers == 0 && !(d.flags & MK_GEMM_SCALED)),
-               "mk_gemm: MK_EPI_SWIGLU needs B2 and K > 0, and takes neither peers nor alpha / beta");
-    MK_REQUIRE((d.flags & ~(uint32_t)(MK_GEMM_SCALED | MK_GEMM_GATE_SIGMOID)) == 0, "mk_gemm: unknown flags 0x%x", d.flags);
-    MK_REQUIRE(!(d.flags & MK_GEMM_GATE_SIGMOID) || d.epilogue == MK_EPI_SWIGLU, "mk_gemm: MK_GEMM_GATE_SIGMOID belongs to MK_EPI_SWIGLU");
-    MK_REQUIRE(d.n_peers >= 0 && d.n_peers <= MK_MAX_PEERS, "mk_gemm: n_peers %d out of range", d.n_peers);
-    for (int i = 0; i < d.n_peers; ++i) MK_REQUIRE(d.peer_C[i], "mk_gemm: peer_C[%d] is null", i);
+    bool nothing_to_do = false;
+    mk_status vs = validate_gemm_desc(d, "mk_gemm", &nothing_to_do);
+    if (vs != MK_OK) return vs;
+    if (nothing_to_do) return MK_OK;
     if (dev->mock) return fail(MK_ERR_CUDA, "mk_gemm: no CUDA device (mock devices run no kernels)");
     MK_CUDA(cudaSetDevice(dev->ordinal));
     bool handled = false;

@@ -353,7 +353,7 @@ mk_status gemm_skinny(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, bo
     do {                                                                                                                           \
         auto kern = gemm_skinny_kernel<BF, DUAL_>;                                                                                 \
         MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring<DUAL_>::SMEM_BYTES));                 \
-        kern<<<grid, THREADS, Ring<DUAL_>::SMEM_BYTES, st>>>(ta, tw, tw2, p, dev->kerr);                                           \
+        kern<<<grid, THREADS, Ring<DUAL_>::SMEM_BYTES, st>>>(ta, tw, tw2, p, stream_kerr(dev, st));                                           \
     } while (0)
         if (dual) { if (bf) MK_SKINNY(true, true); else MK_SKINNY(false, true); }
         else { if (bf) MK_SKINNY(true, false); else MK_SKINNY(false, false); }

@@ -334,8 +334,8 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, int64_t tile_ro
         constexpr int N16 = 32 * ES / 16;              // 16-byte pieces per 32 columns
         uint8_t* stage = stage_out + q * 8192;
         const int64_t row0 = tile_row0 + q * 32;
-#pragma unroll 1
         const int passes = p.dual ? 1 : BN / PASS_COLS;   // gated: 128 output columns, one pass of 256 bytes per row
+#pragma unroll 1
         for (int ps = 0; ps < passes; ++ps) {
             const int64_t pc0 = col0 + ps * PASS_COLS;
             if (pc0 >= p.N) break;  // warp-uniform
@@ -926,7 +926,7 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
         p.n_peers = d.n_peers;
         for (int q = 0; q < d.n_peers; ++q) p.peer_C[q] = (char*)d.peer_C[q] + (size_t)b * d.stride_c * es_out;
         p.staged = staged_ok(p, es_out);
-        p.kerr = dev->kerr;
+        p.kerr = stream_kerr(dev, st);
 
         // Few rows (decoding): one row of 128 x 256 tiles leaves most SMs idle while the work is streaming the
         // weights.  K is then cut into ranges, every (tile, range) unit writes an f32 partial tile to a
@@ -1037,12 +1037,56 @@ mk_status static_setup(int ordinal) {
 }
 
 template <bool TRANS_B, int OUT>
-mk_status launch_tc_static(int sms, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p) {
-    auto kern = gemm_tc_kernel<TRANS_B, OUT>;
-    MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    const int tiles = p.tiles_m * p.tiles_n;
-    kern<<<tiles < sms ? tiles : sms, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+mk_status launch_tc_static(int sms, bool pair, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p) {
+    if (pair) {
+        auto kern = gemm_tc_pair_kernel<TRANS_B, OUT>;
+        MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+        const int tiles = p.tiles_m2 * p.tiles_n;
+        const int clusters = tiles < sms / 2 ? tiles : sms / 2;
+        kern<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(ta, tb, tb, p);
+    } else {
+        auto kern = gemm_tc_kernel<TRANS_B, OUT>;
+        MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        const int tiles = p.tiles_m * p.tiles_n;
+        kern<<<tiles < sms ? tiles : sms, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, p);
+    }
     MK_CUDA(cudaGetLastError());
+    return MK_OK;
+}
+
+// Restores the calling thread's current device on every exit path.
+struct DeviceGuard {
+    int prev = -1;
+    mk_status enter(int ordinal) {
+        MK_CUDA(cudaGetDevice(&prev));
+        if (prev != ordinal) MK_CUDA(cudaSetDevice(ordinal));
+        else prev = -1;
+        return MK_OK;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) {
+            cudaSetDevice(prev);
+            cudaGetLastError();
+        }
+    }
+};
+
+// Waits for the stream and reports the first non-zero word among the first `batch`.
+mk_status read_static_words(KernelError* words, int batch, cudaStream_t stream, uint32_t* kernel_error, const char* who) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    MK_CUDA(cudaStreamIsCapturing(stream, &cs));
+    if (cs != cudaStreamCaptureStatusNone)
+        return fail(MK_ERR_INVALID, "%s: the stream is capturing; the error words can only be read from a stream that runs", who);
+    MK_CUDA(cudaStreamSynchronize(stream));
+    KernelError host[kStaticMaxBatch];
+    MK_CUDA(cudaMemcpy(host, words, sizeof(KernelError) * batch, cudaMemcpyDeviceToHost));
+    *kernel_error = 0;
+    for (int b = 0; b < batch; ++b)
+        if (host[b].code) {
+            *kernel_error = host[b].code;
+            return fail(MK_ERR_KERNEL, "%s: batch item %d reported error word 0x%x (block %u, detail %u)", who, b, host[b].code,
+                        host[b].block, host[b].detail);
+        }
     return MK_OK;
 }
 }  // namespace
@@ -1053,30 +1097,40 @@ extern "C" mk_status mk_gemm_static(int32_t device_ordinal, void* cuda_stream, c
     MK_REQUIRE(desc, "mk_gemm_static: null descriptor");
     MK_REQUIRE(device_ordinal >= 0 && device_ordinal < kMaxDevices, "mk_gemm_static: device ordinal %d out of range", device_ordinal);
     mk_gemm_desc d = *desc;
-    if (d.batch <= 0) d.batch = 1;
+    // the rules of mk_gemm first (dtypes, leading dimensions, epilogue / flag combinations, non-null peers) ...
+    bool nothing_to_do = false;
+    mk_status st = validate_gemm_desc(d, "mk_gemm_static", &nothing_to_do);
+    if (st != MK_OK) return st;
+    // ... then what this entry point adds: the static scratch bounds the batch, and only the tensor-core kernel runs
     if (d.batch > kStaticMaxBatch)
         return fail(MK_ERR_INVALID, "mk_gemm_static: batch %d exceeds the static scratch (one error word per batch item, at most %d)", d.batch,
                     kStaticMaxBatch);
     MK_REQUIRE(d.dtype_in == MK_BF16 || d.dtype_in == MK_F16, "mk_gemm_static: only bf16 / f16 inputs run on the tensor-core kernel");
-    MK_REQUIRE(dtype_valid(d.dtype_out), "mk_gemm_static: unknown output dtype %d", d.dtype_out);
     MK_REQUIRE(d.M > 0 && d.N > 0 && d.K > 0, "mk_gemm_static: M, N, K must be positive");
-    MK_REQUIRE(d.A && d.B && d.C, "mk_gemm_static: null A, B or C");
-    MK_REQUIRE(d.lda >= d.K && d.ldb >= (d.trans_b ? d.K : d.N) && d.ldc >= d.N, "mk_gemm_static: leading dimension too small");
-    MK_REQUIRE(d.epilogue == MK_EPI_NONE || ((d.epilogue == MK_EPI_ADD || d.epilogue == MK_EPI_ADD_ROW) && d.D), "mk_gemm_static: bad epilogue");
-    MK_REQUIRE(d.n_peers >= 0 && d.n_peers <= MK_MAX_PEERS, "mk_gemm_static: n_peers %d out of range", d.n_peers);
+    MK_REQUIRE(d.epilogue != MK_EPI_SWIGLU, "mk_gemm_static: the gated pair of products is not available here; use mk_gemm");
     if ((reinterpret_cast<uintptr_t>(d.A) & 15) || (reinterpret_cast<uintptr_t>(d.B) & 15) || (d.lda % 8) || (d.ldb % 8) || (d.stride_a % 8) ||
         (d.stride_b % 8))
         return fail(MK_ERR_UNSUPPORTED, "mk_gemm_static: A and B need 16-byte aligned bases and row pitches (TMA); use mk_gemm for other layouts");
     MK_REQUIRE(d.M <= 0x7fffff00ll && d.N <= 0x7fffff00ll && d.K <= 0x7fffff00ll, "mk_gemm_static: dimension too large");
     const int64_t tiles_m = (d.M + BM - 1) / BM, tiles_n = (d.N + BN - 1) / BN;
     MK_REQUIRE(tiles_m * tiles_n <= 0x7fffffffll, "mk_gemm_static: too many tiles");
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
 
-    MK_CUDA(cudaSetDevice(device_ordinal));
-    mk_status st = static_setup(device_ordinal);
+    DeviceGuard guard;
+    st = guard.enter(device_ordinal);
+    if (st != MK_OK) return st;
+    if (kernel_error) {     // the synchronous form cannot run inside a capture
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        MK_CUDA(cudaStreamIsCapturing(stream, &cs));
+        if (cs != cudaStreamCaptureStatusNone)
+            return fail(MK_ERR_INVALID, "mk_gemm_static: kernel_error asks for a stream synchronisation, which a capturing stream cannot do; pass NULL");
+    }
+    st = static_setup(device_ordinal);
     if (st != MK_OK) return st;
     if (g_static_cc_major[device_ordinal] != 10) return fail(MK_ERR_UNSUPPORTED, "mk_gemm_static: needs an sm_100 device");
     KernelError* words = g_static_ptr[device_ordinal];
-    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    const int sms = g_static_sms[device_ordinal];
+    const bool pair = use_pair(d, sms);
 
     // The kernel only writes an error word when a wait gives up (compare-and-swap against 0), and the
     // array keeps whatever the previous call left: clear the words this call uses, in stream order.
@@ -1089,7 +1143,7 @@ extern "C" mk_status mk_gemm_static(int32_t device_ordinal, void* cuda_stream, c
         alignas(64) CUtensorMap ta, tb;
         st = encode_2d(&ta, d.dtype_in, A, (uint64_t)d.K, (uint64_t)d.M, (uint64_t)d.lda * 2, BK, BM);
         if (st != MK_OK) return st;
-        st = d.trans_b ? encode_2d(&tb, d.dtype_in, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.ldb * 2, BK, BN)
+        st = d.trans_b ? encode_2d(&tb, d.dtype_in, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.ldb * 2, BK, pair ? BN / 2 : BN)
                        : encode_2d(&tb, d.dtype_in, B, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb * 2, 64, BK);
         if (st != MK_OK) return st;
         TcParams p{};
@@ -1101,16 +1155,18 @@ extern "C" mk_status mk_gemm_static(int32_t device_ordinal, void* cuda_stream, c
         p.scaled = (d.flags & MK_GEMM_SCALED) ? 1 : 0;
         p.alpha = p.scaled ? d.alpha : 1.0f;
         p.beta = p.scaled ? d.beta : 1.0f;
-        p.idesc = idesc_f16(d.dtype_in == MK_BF16 ? 1u : 0u, 0u, d.trans_b ? 0u : 1u, BM, BN);
+        const uint32_t fmt = d.dtype_in == MK_BF16 ? 1u : 0u;
+        p.idesc = idesc_f16(fmt, 0u, d.trans_b ? 0u : 1u, BM, BN);
+        p.idesc2 = idesc_f16(fmt, 0u, d.trans_b ? 0u : 1u, 2 * BM, BN);
         p.tiles_m = (int)tiles_m;
+        p.tiles_m2 = (int)((d.M + 2 * BM - 1) / (2 * BM));
         p.tiles_n = (int)tiles_n;
         p.group_m = group_m_setting();
         p.n_peers = d.n_peers;
         for (int q = 0; q < d.n_peers; ++q) p.peer_C[q] = (char*)d.peer_C[q] + (size_t)b * d.stride_c * es_out;
         p.staged = staged_ok(p, es_out);
         p.kerr = words + b;
-        const int sms = g_static_sms[device_ordinal];
-#define MK_TCS(TB, OUT) st = launch_tc_static<TB, OUT>(sms, stream, ta, tb, p)
+#define MK_TCS(TB, OUT) st = launch_tc_static<TB, OUT>(sms, pair, stream, ta, tb, p)
         if (d.trans_b) {
             if (d.dtype_out == MK_F32) MK_TCS(true, MK_F32); else if (d.dtype_out == MK_BF16) MK_TCS(true, MK_BF16); else MK_TCS(true, MK_F16);
         } else {
@@ -1119,18 +1175,20 @@ extern "C" mk_status mk_gemm_static(int32_t device_ordinal, void* cuda_stream, c
 #undef MK_TCS
         if (st != MK_OK) return st;
     }
-    if (kernel_error) {
-        // Optional check: waits for the stream and reports the first non-zero error word.
-        MK_CUDA(cudaStreamSynchronize(stream));
-        KernelError host[kStaticMaxBatch];
-        MK_CUDA(cudaMemcpy(host, words, sizeof(KernelError) * d.batch, cudaMemcpyDeviceToHost));
-        *kernel_error = 0;
-        for (int b = 0; b < d.batch; ++b)
-            if (host[b].code) {
-                *kernel_error = host[b].code;
-                return fail(MK_ERR_KERNEL, "mk_gemm_static: batch item %d reported error word 0x%x (block %u, detail %u)", b, host[b].code,
-                            host[b].block, host[b].detail);
-            }
-    }
+    if (kernel_error) return read_static_words(words, d.batch, stream, kernel_error, "mk_gemm_static");
     return MK_OK;
+}
+
+extern "C" mk_status mk_gemm_static_status(int32_t device_ordinal, void* cuda_stream, int32_t batch, uint32_t* kernel_error) {
+    using namespace mk;
+    MK_REQUIRE(kernel_error, "mk_gemm_static_status: null output");
+    MK_REQUIRE(device_ordinal >= 0 && device_ordinal < kMaxDevices, "mk_gemm_static_status: device ordinal %d out of range", device_ordinal);
+    if (batch <= 0) batch = 1;
+    MK_REQUIRE(batch <= kStaticMaxBatch, "mk_gemm_static_status: batch %d exceeds the static scratch (at most %d)", batch, kStaticMaxBatch);
+    DeviceGuard guard;
+    mk_status st = guard.enter(device_ordinal);
+    if (st != MK_OK) return st;
+    st = static_setup(device_ordinal);
+    if (st != MK_OK) return st;
+    return read_static_words(g_static_ptr[device_ordinal], batch, static_cast<cudaStream_t>(cuda_stream), kernel_error, "mk_gemm_static_status");
 }

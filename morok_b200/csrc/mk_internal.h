@@ -67,24 +67,49 @@ enum : unsigned int {
 }  // namespace mk
 
 // ---- opaque handle definitions -------------------------------------------------------------------
+namespace mk {
+// An event recorded on one stream when a block went back to the allocator cache; shared by every block
+// parked since the stream last received work.
+struct StreamFence {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t event = nullptr;
+    ~StreamFence() {
+        if (event) cudaEventDestroy(event);
+    }
+};
+// What the library keeps per CUDA stream it has enqueued work on.  `slot` indexes the device arrays of
+// kernel error words and claim counters, so that launches on different streams (and recorded plans, which
+// own their capture stream for life) never share either.
+struct StreamState {
+    int slot = 0;                          // 0 is also the shared fallback when every slot is taken
+    void* scratch = nullptr;               // two-launch kernels (K-split GEMM, key-split attention): grown on demand
+    size_t scratch_bytes = 0;
+    bool dirty = false;                    // work was enqueued since the last fence
+    bool plan = false;                     // capture stream of a recorded plan
+    std::shared_ptr<StreamFence> fence;    // completes when everything enqueued before the last release has run
+};
+}  // namespace mk
+
 struct mk_device {
     int ordinal = 0;
     bool mock = false;  // host-memory stand-in for allocator / copy tests; cannot run kernels
     cudaDeviceProp prop{};
-    std::mutex mu;  // guards the allocator state below
-    // LRU free lists keyed by allocation size; each list newest-first, at most kMaxPerKey entries.
-    std::map<size_t, std::list<void*>> free_lists;
+    std::mutex mu;  // guards the allocator state, the stream table and the tuning records below
+    // LRU free lists keyed by allocation size; each list newest-first, at most kMaxPerKey entries.  A parked
+    // block carries the fences of the streams that may still be using it (stream-ordered reuse).
+    struct Parked {
+        void* ptr;
+        std::vector<std::shared_ptr<mk::StreamFence>> fences;
+    };
+    std::map<size_t, std::list<Parked>> free_lists;
     mk_alloc_stats_t stats{};
     int inject_oom = 0;
-    // kernel error word (device memory)
-    mk::KernelError* kerr = nullptr;
-    // claim counters of persistent kernels: a ring of slots, one zeroed (in stream order) per launch
-    unsigned int* work_counters = nullptr;
-    std::atomic<uint32_t> work_counter_next{0};
-    static constexpr uint32_t kWorkCounterSlots = 256;
-    // Scratch of kernels that work in two launches (K-split GEMM, key-split attention): one block per
-    // stream, grown on demand and reused in stream order, so launches on different streams never share it.
-    std::map<cudaStream_t, std::pair<void*, size_t>> stream_scratch;
+    // per-stream slots (device memory): kernel error words and the claim counters of persistent kernels
+    static constexpr int kStreamSlots = 256;
+    mk::KernelError* kerr_words = nullptr;      // [kStreamSlots]
+    unsigned int* work_counters = nullptr;      // [kStreamSlots], one zeroed (in stream order) per launch
+    std::map<cudaStream_t, mk::StreamState> streams;
+    std::vector<int> free_slots;                // slots 1 .. kStreamSlots-1 not in use
     std::vector<void*> retired_scratch;   // outgrown blocks: work already enqueued (or recorded in a plan) may still use them
     // schedule choices found by mk_gemm_autotune (or loaded from a file), keyed by the problem; guarded by mu
     std::map<std::array<int64_t, 9>, mk_gemm_tuning> gemm_tunes;
@@ -129,6 +154,9 @@ mk_status device_alloc(mk_device* dev, size_t bytes, uint32_t flags, void** out)
 void device_release(mk_device* dev, void* ptr, size_t bytes);
 mk_status buf_ptr(mk_buf* b, void** out);
 
+// Descriptor rules shared by mk_gemm and mk_gemm_static (dispatch.cpp).
+mk_status validate_gemm_desc(mk_gemm_desc& d, const char* who, bool* nothing_to_do);
+
 // kernel launchers implemented in the .cu files
 mk_status gemm_simt(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d);
 mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, bool* handled);
@@ -143,8 +171,26 @@ bool gemm_tuning_for(mk_device* dev, const mk_gemm_desc& d, mk_gemm_tuning* out)
 void note_launch(mk_device* dev, cudaStream_t st, const char* name);
 // At least `bytes` of device memory that belongs to work enqueued on `st` (valid until the next call for the same stream).
 mk_status stream_scratch(mk_device* dev, cudaStream_t st, size_t bytes, void** out);
-// Frees the scratch block of a stream that is about to be destroyed (cudaFree waits for work that still uses it).
-void release_stream_scratch(mk_device* dev, cudaStream_t st);
+// The error word and the claim counter of the stream's slot (device pointers).
+KernelError* stream_kerr(mk_device* dev, cudaStream_t st);
+unsigned int* stream_work_counter(mk_device* dev, cudaStream_t st);
+// Marks the stream as carrying work the allocator must order block reuse after (launches do this through
+// note_launch; copies and memsets call it directly).
+void touch_stream(mk_device* dev, cudaStream_t st);
+// Marks the stream as the capture stream of a recorded plan (its error word is reported by every status query).
+void mark_plan_stream(mk_device* dev, cudaStream_t st);
+// Drops everything kept for a stream that is about to be destroyed: scratch block (cudaFree waits for work
+// that still uses it), slot, fence.
+void release_stream_state(mk_device* dev, cudaStream_t st);
+// While alive, allocations made by the calling thread are ordered on `st`: a cached block that another
+// stream may still be using makes `st` wait for that stream's fence instead of blocking the host, and
+// zero-initialisation runs on `st`.
+struct AllocStreamScope {
+    explicit AllocStreamScope(cudaStream_t st);
+    ~AllocStreamScope();
+    bool prev_set;
+    cudaStream_t prev;
+};
 
 mk_status ew_silu(mk_device* dev, cudaStream_t s, int32_t dtype, const void* x, void* y, int64_t n);
 mk_status ew_sigmoid(mk_device* dev, cudaStream_t s, int32_t dtype, const void* x, void* y, int64_t n);

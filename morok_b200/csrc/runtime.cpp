@@ -74,21 +74,93 @@ static cudaError_t raw_stream_sync(mk_device* dev, cudaStream_t st) {
     return cudaStreamSynchronize(st);
 }
 
+// ---- stream-ordered reuse ------------------------------------------------------------------------------
+// The reference's LRU allocator hands a cached block to the next caller at once and leaves ordering to its
+// scheduler ("scheduler guarantees exclusive access", device/src/allocator.rs:72-112); its CUDA calls all
+// run on one stream.  Here kernels run on several non-blocking streams, so a parked block remembers, per
+// stream that had work in flight when it was released, an event behind that work; whoever takes the block
+// from the cache waits for the events of the other streams first (on the consumer's stream when the
+// calling thread declared one with AllocStreamScope, else on the host -- usually the events have long
+// completed and the query costs a microsecond).
+static thread_local bool t_alloc_set = false;
+static thread_local cudaStream_t t_alloc_stream = nullptr;
+
+AllocStreamScope::AllocStreamScope(cudaStream_t st) : prev_set(t_alloc_set), prev(t_alloc_stream) {
+    t_alloc_set = true;
+    t_alloc_stream = st;
+}
+AllocStreamScope::~AllocStreamScope() {
+    t_alloc_set = prev_set;
+    t_alloc_stream = prev;
+}
+
+static bool stream_is_capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+// Fences of every stream that may still be working on memory released now (caller holds dev->mu).
+static void collect_fences_locked(mk_device* dev, std::vector<std::shared_ptr<StreamFence>>* out) {
+    if (dev->mock) return;
+    for (auto& kv : dev->streams) {
+        StreamState& ss = kv.second;
+        if (ss.dirty) {
+            if (stream_is_capturing(kv.first)) continue;     // recorded work runs later; a plan retains what it uses
+            auto f = std::make_shared<StreamFence>();
+            f->stream = kv.first;
+            if (cudaEventCreateWithFlags(&f->event, cudaEventDisableTiming) != cudaSuccess || cudaEventRecord(f->event, kv.first) != cudaSuccess) {
+                cudaGetLastError();
+                cudaStreamSynchronize(kv.first);             // no event to be had: make the release itself safe
+                cudaGetLastError();
+                f.reset();
+            }
+            ss.fence = f;
+            ss.dirty = false;
+        }
+        if (ss.fence) out->push_back(ss.fence);
+    }
+}
+
+// Orders the calling thread's next use of a block after the work its fences stand for.
+static void wait_fences(const std::vector<std::shared_ptr<StreamFence>>& fences) {
+    for (const auto& f : fences) {
+        if (!f || !f->event) continue;
+        if (t_alloc_set && f->stream == t_alloc_stream) continue;        // same queue: already ordered
+        cudaError_t q = cudaEventQuery(f->event);
+        if (q == cudaSuccess) continue;
+        cudaGetLastError();
+        if (t_alloc_set && !stream_is_capturing(t_alloc_stream)) cudaStreamWaitEvent(t_alloc_stream, f->event, 0);
+        else cudaEventSynchronize(f->event);
+        cudaGetLastError();
+    }
+}
+
 // cudaMalloc with the reference's LRU policy in front of it (device/src/allocator.rs:383-442):
 // reuse a cached block of the same size class, else allocate; on out-of-memory flush the whole
 // cache and retry once.
 mk_status device_alloc(mk_device* dev, size_t bytes, uint32_t flags, void** out) {
     const size_t key = size_key(bytes);
     void* p = nullptr;
+    std::vector<std::shared_ptr<StreamFence>> fences;
     {
         std::lock_guard<std::mutex> lk(dev->mu);
         auto it = dev->free_lists.find(key);
         if (it != dev->free_lists.end() && !it->second.empty()) {
-            p = it->second.front();
+            p = it->second.front().ptr;
+            fences = std::move(it->second.front().fences);
             it->second.pop_front();
             dev->stats.cache_hits++;
             dev->stats.bytes_cached -= key;
         }
+    }
+    if (p && !fences.empty()) {
+        cudaSetDevice(dev->ordinal);
+        wait_fences(fences);
+        fences.clear();
     }
     if (!p) {
         if (!dev->mock) MK_CUDA(cudaSetDevice(dev->ordinal));
@@ -107,13 +179,13 @@ mk_status device_alloc(mk_device* dev, size_t bytes, uint32_t flags, void** out)
             {
                 std::lock_guard<std::mutex> lk(dev->mu);
                 for (auto& kv : dev->free_lists)
-                    for (void* v : kv.second) victims.push_back(v);
+                    for (auto& v : kv.second) victims.push_back(v.ptr);
                 dev->free_lists.clear();
                 dev->stats.bytes_cached = 0;
                 dev->stats.oom_flushes++;
                 dev->stats.device_frees += victims.size();
             }
-            for (void* v : victims) raw_free(dev, v);
+            for (void* v : victims) raw_free(dev, v);       // cudaFree waits for work that still uses the block
             bool injected_again = false;
             {
                 std::lock_guard<std::mutex> lk(dev->mu);
@@ -133,7 +205,18 @@ mk_status device_alloc(mk_device* dev, size_t bytes, uint32_t flags, void** out)
         dev->stats.device_allocs++;
     }
     if (flags & MK_ALLOC_ZERO_INIT) {
-        cudaError_t e = raw_memset0(dev, p, key);
+        // Zeroed on the consumer's stream when the thread declared one, else finished before this returns, so that
+        // the zeros are in place whichever stream touches the buffer first.
+        cudaError_t e;
+        if (dev->mock) {
+            e = raw_memset0(dev, p, key);
+        } else if (t_alloc_set) {
+            e = cudaMemsetAsync(p, 0, key, t_alloc_stream);
+            touch_stream(dev, t_alloc_stream);
+        } else {
+            e = cudaMemsetAsync(p, 0, key, (cudaStream_t)0);
+            if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)0);
+        }
         if (e != cudaSuccess) {
             device_release(dev, p, bytes);
             return cuda_fail(e, "cudaMemset(zero_init)");
@@ -152,12 +235,15 @@ void device_release(mk_device* dev, void* ptr, size_t bytes) {
     if (!ptr) return;
     const size_t key = size_key(bytes);
     bool park = false;
+    if (!dev->mock) cudaSetDevice(dev->ordinal);
     {
         std::lock_guard<std::mutex> lk(dev->mu);
         if (dev->stats.bytes_in_use >= key) dev->stats.bytes_in_use -= key;
         auto& lst = dev->free_lists[key];
         if (lst.size() < mk_device::kMaxPerKey) {
-            lst.push_front(ptr);
+            mk_device::Parked blk{ptr, {}};
+            collect_fences_locked(dev, &blk.fences);
+            lst.push_front(std::move(blk));
             dev->stats.cache_returns++;
             dev->stats.bytes_cached += key;
             park = true;
@@ -197,7 +283,7 @@ using namespace mk;
 extern "C" {
 
 const char* mk_last_error(void) { return g_err; }
-int32_t mk_abi_version(void) { return 3; }
+int32_t mk_abi_version(void) { return 4; }
 int32_t mk_abi_struct_size(int32_t which) {
     return which == 0 ? (int32_t)sizeof(mk_gemm_desc) : which == 1 ? (int32_t)sizeof(mk_sdpa_desc) : -1;
 }
@@ -226,10 +312,11 @@ mk_status mk_device_open(int32_t ordinal, mk_device** out) {
     std::unique_ptr<mk_device> dev(new mk_device());
     dev->ordinal = ordinal;
     MK_CUDA(cudaGetDeviceProperties(&dev->prop, ordinal));
-    MK_CUDA(cudaMalloc((void**)&dev->kerr, sizeof(KernelError)));
-    MK_CUDA(cudaMemset(dev->kerr, 0, sizeof(KernelError)));
-    MK_CUDA(cudaMalloc((void**)&dev->work_counters, sizeof(unsigned int) * mk_device::kWorkCounterSlots));
-    MK_CUDA(cudaMemset(dev->work_counters, 0, sizeof(unsigned int) * mk_device::kWorkCounterSlots));
+    MK_CUDA(cudaMalloc((void**)&dev->kerr_words, sizeof(KernelError) * mk_device::kStreamSlots));
+    MK_CUDA(cudaMemset(dev->kerr_words, 0, sizeof(KernelError) * mk_device::kStreamSlots));
+    MK_CUDA(cudaMalloc((void**)&dev->work_counters, sizeof(unsigned int) * mk_device::kStreamSlots));
+    MK_CUDA(cudaMemset(dev->work_counters, 0, sizeof(unsigned int) * mk_device::kStreamSlots));
+    for (int i = mk_device::kStreamSlots - 1; i >= 1; --i) dev->free_slots.push_back(i);
     *out = dev.release();
     return MK_OK;
 }
@@ -251,9 +338,11 @@ mk_status mk_device_close(mk_device* dev) {
         cudaDeviceSynchronize();
     }
     mk_alloc_trim(dev);
-    if (dev->kerr) cudaFree(dev->kerr);
+    if (dev->kerr_words) cudaFree(dev->kerr_words);
     if (dev->work_counters) cudaFree(dev->work_counters);
-    for (auto& kv : dev->stream_scratch) cudaFree(kv.second.first);
+    for (auto& kv : dev->streams)
+        if (kv.second.scratch) cudaFree(kv.second.scratch);
+    dev->streams.clear();
     for (void* p : dev->retired_scratch) cudaFree(p);
     cudaGetLastError();
     delete dev;
@@ -295,7 +384,7 @@ mk_status mk_stream_create(mk_device* dev, mk_stream** out) {
 
 mk_status mk_stream_destroy(mk_stream* s) {
     MK_REQUIRE(s, "mk_stream_destroy: null stream");
-    if (s->dev && !s->dev->mock) mk::release_stream_scratch(s->dev, s->s);
+    if (s->dev && !s->dev->mock) mk::release_stream_state(s->dev, s->s);
     cudaError_t e = cudaStreamDestroy(s->s);
     delete s;
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamDestroy");
@@ -435,7 +524,7 @@ mk_status mk_alloc_trim(mk_device* dev) {
     {
         std::lock_guard<std::mutex> lk(dev->mu);
         for (auto& kv : dev->free_lists)
-            for (void* v : kv.second) victims.push_back(v);
+            for (auto& v : kv.second) victims.push_back(v.ptr);
         dev->free_lists.clear();
         dev->stats.bytes_cached = 0;
         dev->stats.device_frees += victims.size();
@@ -463,6 +552,7 @@ mk_status mk_copy_h2d(mk_buf* dst, const void* src, size_t bytes, mk_stream* s) 
     mk_status st = buf_ptr(dst, &d);
     if (st != MK_OK) return st;
     MK_CUDA(raw_copy(dst->data->dev, d, src, bytes, cudaMemcpyHostToDevice, raw(s)));
+    touch_stream(dst->data->dev, raw(s));
     return MK_OK;
 }
 
@@ -496,6 +586,7 @@ static mk_status copy_dd(mk_buf* dst, mk_buf* src, size_t bytes, mk_stream* s, c
     st = buf_ptr(src, &p);
     if (st != MK_OK) return st;
     MK_CUDA(raw_copy(dst->data->dev, d, p, bytes, cudaMemcpyDefault, raw(s)));
+    touch_stream(dst->data->dev, raw(s));
     return MK_OK;
 }
 
@@ -536,6 +627,31 @@ mk_status mk_memcpy_async(mk_device* dev, void* dst, const void* src, size_t byt
     MK_REQUIRE(dst && src, "mk_memcpy_async: null pointer");
     static const cudaMemcpyKind kinds[3] = {cudaMemcpyHostToDevice, cudaMemcpyDeviceToHost, cudaMemcpyDeviceToDevice};
     MK_CUDA(cudaMemcpyAsync(dst, src, bytes, kinds[kind], raw(s)));
+    touch_stream(dev, raw(s));
+    return MK_OK;
+}
+
+// CudaAllocator::memset_zeros (device/src/allocator.rs:256-309) generalised to any byte value.
+mk_status mk_memset_async(mk_device* dev, void* dst, int32_t byte_value, size_t bytes, mk_stream* s) {
+    MK_REQUIRE(dev, "mk_memset_async: null device");
+    MK_REQUIRE(byte_value >= 0 && byte_value <= 255, "mk_memset_async: byte value %d", byte_value);
+    if (bytes == 0) return MK_OK;
+    MK_REQUIRE(dst, "mk_memset_async: null pointer");
+    if (dev->mock) {
+        memset(dst, byte_value, bytes);
+        return MK_OK;
+    }
+    MK_CUDA(cudaSetDevice(dev->ordinal));
+    MK_CUDA(cudaMemsetAsync(dst, byte_value, bytes, raw(s)));
+    touch_stream(dev, raw(s));
+    return MK_OK;
+}
+
+mk_status mk_mem_info(mk_device* dev, size_t* free_bytes, size_t* total_bytes) {
+    MK_REQUIRE(dev && free_bytes && total_bytes, "mk_mem_info: null argument");
+    if (dev->mock) return fail(MK_ERR_CUDA, "mk_mem_info: mock device has no device memory");
+    MK_CUDA(cudaSetDevice(dev->ordinal));
+    MK_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
     return MK_OK;
 }
 
@@ -587,6 +703,7 @@ mk_status mk_all_gather_push(mk_device* dev, mk_stream* s, const void* src, size
         if ((const void*)d == src) continue;
         MK_CUDA(cudaMemcpyAsync(d, src, bytes, cudaMemcpyDefault, raw(s)));
     }
+    touch_stream(dev, raw(s));
     return MK_OK;
 }
 
@@ -601,6 +718,7 @@ mk_status mk_all_gather_push_2d(mk_device* dev, mk_stream* s, const void* src, s
         if ((const void*)d == src) continue;
         MK_CUDA(cudaMemcpy2DAsync(d, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDefault, raw(s)));
     }
+    touch_stream(dev, raw(s));
     return MK_OK;
 }
 
@@ -608,12 +726,28 @@ mk_status mk_all_gather_push_2d(mk_device* dev, mk_stream* s, const void* src, s
 mk_status mk_kernel_status(mk_device* dev, mk_stream* s, uint32_t* code) {
     MK_REQUIRE(dev, "mk_kernel_status: null device");
     if (dev->mock) return fail(MK_ERR_CUDA, "mk_kernel_status: mock device runs no kernels");
+    MK_CUDA(cudaSetDevice(dev->ordinal));
     MK_CUDA(cudaStreamSynchronize(raw(s)));
-    KernelError h{};
-    MK_CUDA(cudaMemcpy(&h, dev->kerr, sizeof(h), cudaMemcpyDeviceToHost));
-    if (code) *code = h.code;
-    if (h.code != 0) {
-        cudaMemset(dev->kerr, 0, sizeof(h));
+    // Every stream has its own word.  This query reports the word of `s` and the words of recorded plans
+    // (their kernels write to the slot of the plan's capture stream whichever stream replays them); words of
+    // other streams are left for the queries of those streams.
+    std::vector<int> slots;
+    {
+        std::lock_guard<std::mutex> lk(dev->mu);
+        auto it = dev->streams.find(raw(s));
+        slots.push_back(it != dev->streams.end() ? it->second.slot : 0);
+        for (auto& kv : dev->streams)
+            if (kv.second.plan && kv.second.slot != slots[0]) slots.push_back(kv.second.slot);
+    }
+    static thread_local std::vector<KernelError> host;
+    host.resize(mk_device::kStreamSlots);
+    MK_CUDA(cudaMemcpy(host.data(), dev->kerr_words, sizeof(KernelError) * mk_device::kStreamSlots, cudaMemcpyDeviceToHost));
+    if (code) *code = 0;
+    for (int slot : slots) {
+        const KernelError h = host[slot];
+        if (h.code == 0) continue;
+        if (code) *code = h.code;
+        cudaMemset(dev->kerr_words + slot, 0, sizeof(KernelError));
         return fail(MK_ERR_KERNEL, "kernel error word 0x%x (block %u, detail %u): a bounded pipeline wait gave up", h.code,
                     h.block, h.detail);
     }
@@ -696,31 +830,69 @@ mk_status mk_launch(mk_function* f_, const uint32_t grid[3], const uint32_t bloc
 
 }  // extern "C"
 
-// ---- per-stream scratch ------------------------------------------------------------------------------------------
+// ---- per-stream state: slot (error word, claim counter), scratch, fence ------------------------------------------
 namespace mk {
+// Caller holds dev->mu.
+static StreamState& stream_state_locked(mk_device* dev, cudaStream_t st) {
+    auto it = dev->streams.find(st);
+    if (it != dev->streams.end()) return it->second;
+    StreamState ss;
+    if (st != nullptr && !dev->free_slots.empty()) {     // the legacy stream keeps slot 0; so does everyone once the slots run out
+        ss.slot = dev->free_slots.back();
+        dev->free_slots.pop_back();
+    }
+    return dev->streams.emplace(st, std::move(ss)).first->second;
+}
+
 mk_status stream_scratch(mk_device* dev, cudaStream_t st, size_t bytes, void** out) {
     std::lock_guard<std::mutex> lk(dev->mu);
-    auto& slot = dev->stream_scratch[st];
-    if (slot.second < bytes) {
+    StreamState& ss = stream_state_locked(dev, st);
+    if (ss.scratch_bytes < bytes) {
         // Growing: work already enqueued on this stream, or recorded in a plan, may still use the old block,
         // so it is kept until the device is closed (no synchronisation here: this also runs during capture).
-        if (slot.first) dev->retired_scratch.push_back(slot.first);
-        slot = {nullptr, 0};
+        if (ss.scratch) dev->retired_scratch.push_back(ss.scratch);
+        ss.scratch = nullptr;
+        ss.scratch_bytes = 0;
         const size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);   // whole MiB
         void* p = nullptr;
         MK_CUDA(cudaMalloc(&p, want));
-        slot = {p, want};
+        ss.scratch = p;
+        ss.scratch_bytes = want;
     }
-    *out = slot.first;
+    *out = ss.scratch;
     return MK_OK;
 }
 
-void release_stream_scratch(mk_device* dev, cudaStream_t st) {
+KernelError* stream_kerr(mk_device* dev, cudaStream_t st) {
     std::lock_guard<std::mutex> lk(dev->mu);
-    auto it = dev->stream_scratch.find(st);
-    if (it == dev->stream_scratch.end()) return;
-    if (it->second.first) cudaFree(it->second.first);
-    dev->stream_scratch.erase(it);
+    return dev->kerr_words + stream_state_locked(dev, st).slot;
+}
+
+unsigned int* stream_work_counter(mk_device* dev, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(dev->mu);
+    return dev->work_counters + stream_state_locked(dev, st).slot;
+}
+
+void touch_stream(mk_device* dev, cudaStream_t st) {
+    if (dev->mock) return;
+    std::lock_guard<std::mutex> lk(dev->mu);
+    stream_state_locked(dev, st).dirty = true;
+}
+
+void mark_plan_stream(mk_device* dev, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(dev->mu);
+    stream_state_locked(dev, st).plan = true;
+}
+
+void release_stream_state(mk_device* dev, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(dev->mu);
+    auto it = dev->streams.find(st);
+    if (it == dev->streams.end()) return;
+    if (it->second.scratch) cudaFree(it->second.scratch);
+    if (it->second.slot != 0) dev->free_slots.push_back(it->second.slot);
+    // Parked blocks may still hold this stream's fence: the event stays valid after the stream is destroyed
+    // (work that was enqueued still completes), so waiting on it later is fine.
+    dev->streams.erase(it);
 }
 }  // namespace mk
 
@@ -751,6 +923,7 @@ void drop_profile() {
 
 void note_launch(mk_device* dev, cudaStream_t st, const char* name) {
     dev->launches++;
+    touch_stream(dev, st);
     LaunchProfile* p = t_profile;
     if (!p || p->dev != dev || p->stream != st) return;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;

@@ -698,10 +698,11 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     p.stage_o = d.n_peers > 0 || getenv("MOROK_B200_ATTN_STAGE_O") != nullptr;
     p.n_peers = d.n_peers;
     for (int i = 0; i < d.n_peers; ++i) p.peer_O[i] = d.peer_O[i];
-    p.kerr = dev->kerr;
-    // A fresh claim counter for this launch, zeroed in stream order (launches on different streams
-    // get different slots of the ring).
-    p.work_counter = dev->work_counters + (dev->work_counter_next.fetch_add(1) % mk_device::kWorkCounterSlots);
+    p.kerr = stream_kerr(dev, st);
+    // The claim counter of this stream, zeroed in stream order before the launch.  Launches on one stream
+    // run one after the other; other streams -- and recorded plans, which keep their capture stream for
+    // life -- have counters of their own, so concurrent kernels never consume each other's claims.
+    p.work_counter = stream_work_counter(dev, st);
     MK_CUDA(cudaMemsetAsync(p.work_counter, 0, sizeof(unsigned int), st));
 
     auto launch = [&](auto kernel, int smem_bytes) -> cudaError_t {

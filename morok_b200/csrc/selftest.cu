@@ -48,7 +48,7 @@ extern "C" mk_status mk_selftest_bounded_wait(mk_device* dev, mk_stream* s, uint
     void* out_ptr = nullptr;
     st = mk_buf_ptr(out, &out_ptr);
     if (st != MK_OK) { mk_free(out); return st; }
-    bounded_wait_selftest_kernel<<<1, 32, 0, raw(s)>>>(dev->kerr, (uint64_t)limit_ms * 1000000ull, (uint32_t*)out_ptr);
+    bounded_wait_selftest_kernel<<<1, 32, 0, raw(s)>>>(stream_kerr(dev, raw(s)), (uint64_t)limit_ms * 1000000ull, (uint32_t*)out_ptr);
     cudaError_t e = cudaGetLastError();
     note_launch(dev, raw(s), "bounded_wait_selftest");
     uint32_t outcome = 0;

@@ -53,6 +53,10 @@ struct Node {
     std::vector<int64_t> view_shape;   // == shape
     std::vector<int32_t> perm;         // non-empty: permute of input axes; empty: reshape
     int32_t last_launches = 0;
+    // Set while a plan was being recorded: the node has a buffer but no data until the plan has run once
+    // (the flag is the plan's "has run" marker, shared by every node the recording realized).
+    std::shared_ptr<std::atomic<bool>> plan_ran;
+    bool has_data() const { return realized && (!plan_ran || plan_ran->load()); }
 
     int64_t numel() const {
         int64_t n = 1;
@@ -89,6 +93,7 @@ bool is_contiguous(const Node& n) {
 // the allocator cache nor be handed to anyone else for as long as the plan lives.
 thread_local mk_stream* t_stream = nullptr;
 thread_local std::vector<std::shared_ptr<mk_buf>>* t_retain = nullptr;
+thread_local std::shared_ptr<std::atomic<bool>> t_plan_ran;      // the recording plan's marker (null outside recording)
 
 std::shared_ptr<mk_buf> make_buf(mk_device* dev, size_t bytes, mk_status* st) {
     mk_buf* b = nullptr;
@@ -103,6 +108,8 @@ mk_status node_ptr(const Node& n, void** out) {
     void* base = nullptr;
     mk_status st = n.numel() == 0 ? MK_OK : buf_ptr(n.buf.get(), &base);
     if (st != MK_OK) return st;
+    // a recording plan bakes this address into its kernels: keep the buffer (leaf inputs included) alive with the plan
+    if (t_retain && n.buf && (t_retain->empty() || t_retain->back() != n.buf)) t_retain->push_back(n.buf);
     *out = base ? (char*)base + n.offset * (int64_t)dtype_size(n.dtype) : nullptr;
     return MK_OK;
 }
@@ -139,6 +146,7 @@ mk_status dense(const NodeP& n, NodeP* out) {
     st = strided_copy(n->dev, raw(t_stream), (int)dtype_size(n->dtype), src, dst, n->ndim(), n->shape.data(), n->strides.data());
     if (st != MK_OK) return st;
     c->realized = true;
+    c->plan_ran = t_plan_ran;
     *out = c;
     return MK_OK;
 }
@@ -388,7 +396,12 @@ mk_status run_binary(Node& n) {
 
 mk_status realize(const NodeP& np) {
     Node& n = *np;
-    if (n.realized) return MK_OK;
+    if (n.realized) {
+        // recorded by a plan that has not run yet: the buffer holds nothing (fine for that plan's own recording)
+        if (!n.has_data() && n.plan_ran != t_plan_ran)
+            return fail(MK_ERR_NOT_ALLOCATED, "realize: an input was recorded into a plan that has not been launched yet; it holds no data");
+        return MK_OK;
+    }
     if (n.dev->mock && n.op != VIEW) return fail(MK_ERR_CUDA, "realize: no CUDA device (mock devices run no kernels)");
     mk_status st = MK_OK;
     switch (n.op) {
@@ -402,6 +415,7 @@ mk_status realize(const NodeP& np) {
                 if (src->op == SDPA && !src->realized && n.perm.size() == 4 && std::equal(n.perm.begin(), n.perm.end(), kSwap)) {
                     if ((st = run_sdpa(*src, true)) != MK_OK) return st;
                     src->realized = true;
+                    src->plan_ran = t_plan_ran;
                     src->in.clear();
                 }
                 if ((st = realize(src)) != MK_OK) return st;
@@ -488,6 +502,7 @@ mk_status realize(const NodeP& np) {
     }
     if (st != MK_OK) return st;
     n.realized = true;
+    n.plan_ran = t_plan_ran;
     n.in.clear();   // a realized tensor is a buffer; its producers can go back to the cache
     return MK_OK;
 }
@@ -510,6 +525,7 @@ struct mk_tensor {
 };
 
 struct mk_plan {
+    std::shared_ptr<std::atomic<bool>> ran = std::make_shared<std::atomic<bool>>(false);   // set by the first launch
     mk_device* dev = nullptr;
     mk_stream capture{nullptr, nullptr};              // the stream the plan was recorded on
     cudaGraphExec_t exec = nullptr;
@@ -748,6 +764,7 @@ mk_status mk_tensor_realize(mk_tensor* t) {
     MK_REQUIRE(t, "mk_tensor_realize: null tensor");
     Node& n = *t->node;
     const uint64_t before = n.dev->launches.load();
+    AllocStreamScope scope(raw(t_stream));      // buffers taken from the cache are ordered on the realising stream
     mk_status st = realize(t->node);
     n.last_launches = (int32_t)(n.dev->launches.load() - before);
     return st;
@@ -763,6 +780,7 @@ mk_status mk_tensor_copyout(mk_tensor* t, void* dst, size_t bytes) {
     MK_REQUIRE(t && (dst || bytes == 0), "mk_tensor_copyout: null argument");
     NodeP n = t->node;
     if (!n->realized) return fail(MK_ERR_NOT_ALLOCATED, "as_vec: tensor is not realized; call realize() first");
+    if (!n->has_data()) return fail(MK_ERR_NOT_ALLOCATED, "as_vec: the tensor was recorded into a plan that has not been launched yet");
     const size_t want = (size_t)n->numel() * dtype_size(n->dtype);
     if (bytes != want) return fail(MK_ERR_SIZE_MISMATCH, "as_vec: %zu bytes requested, tensor holds %zu", bytes, want);
     if (want == 0) return MK_OK;
@@ -807,12 +825,19 @@ mk_status mk_tensor_compile(mk_tensor* t, mk_plan** out) {
         delete plan;
         return fail(MK_ERR_CUDA, "mk_tensor_compile: %s", cudaGetErrorString(e));
     }
+    mark_plan_stream(dev, plan->capture.s);     // own error word and claim counter for the plan's kernels
     t_stream = &plan->capture;
     t_retain = &plan->retained;
+    t_plan_ran = plan->ran;
     const uint64_t before = dev->launches.load();
-    mk_status st = realize(n);
+    mk_status st;
+    {
+        AllocStreamScope scope(plan->capture.s);
+        st = realize(n);
+    }
     t_stream = nullptr;
     t_retain = nullptr;
+    t_plan_ran.reset();
     cudaGraph_t graph = nullptr;
     e = cudaStreamEndCapture(plan->capture.s, &graph);
     if (st == MK_OK && e != cudaSuccess) st = fail(MK_ERR_CUDA, "mk_tensor_compile: capture failed: %s", cudaGetErrorString(e));
@@ -838,6 +863,8 @@ mk_status mk_plan_launch(mk_plan* plan, mk_stream* s) {
     MK_REQUIRE(plan && plan->exec, "mk_plan_launch: null plan");
     MK_CUDA(cudaSetDevice(plan->dev->ordinal));
     MK_CUDA(cudaGraphLaunch(plan->exec, raw(s)));
+    touch_stream(plan->dev, raw(s));
+    plan->ran->store(true);
     plan->dev->launches += (uint64_t)plan->kernels;
     return MK_OK;
 }
@@ -852,7 +879,7 @@ mk_status mk_plan_free(mk_plan* plan) {
     if (!plan) return MK_OK;
     if (plan->exec) cudaGraphExecDestroy(plan->exec);
     if (plan->capture.s) {
-        release_stream_scratch(plan->dev, plan->capture.s);     // scratch the recorded two-launch kernels used
+        release_stream_state(plan->dev, plan->capture.s);     // scratch, error word and claim counter of the recorded kernels
         cudaStreamDestroy(plan->capture.s);
     }
     delete plan;     // releases the retained buffers to the allocator cache

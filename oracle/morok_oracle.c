@@ -144,6 +144,19 @@ ORC_API int orc_max_threads(void) {
 #endif
 }
 
+/* Sets the number of threads later parallel regions use (what MOROK_THREADS / the host's core count  */
+/* decides in the reference, runtime/src/devices/cpu.rs:41-49).  A launcher may have exported          */
+/* OMP_NUM_THREADS=1 into the process; a timing harness calls this with the core count it wants.       */
+ORC_API int orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* matmul: C[m,n] = sum_k A[m,k] * B[k,n]                                                       */
 /*   graph: tensor/src/matmul.rs:82-110 (reshape, transpose, broadcast MUL, sum(-1));           */

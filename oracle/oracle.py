@@ -74,6 +74,8 @@ def _bind(l: C.CDLL) -> C.CDLL:
     l.orc_thread_count.argtypes = [i64, i64, i32]
     l.orc_thread_count.restype = i32
     l.orc_max_threads.restype = i32
+    l.orc_set_threads.argtypes = [i32]
+    l.orc_set_threads.restype = i32
     return l
 
 
@@ -360,10 +362,21 @@ def decoder_layer_f32(x_bits, w, batch, seq, n_q, n_kv, head_dim, eps=1e-5, thet
     API implies (rms_norm: tensor/src/nn/norm.rs:92-110; matmul: tensor/src/matmul.rs:82-110;
     apply_rotary_emb split-half: tensor/src/transformer.rs:32-69; GQA expansion:
     onnx/src/registry/transformer.rs:80-103; attention: tensor/src/transformer.rs:78-137; silu:
-    tensor/src/activation.rs:309-318).  Evaluated in f32 on bf16-rounded x and weights.  With
-    ``round_boundaries`` every op boundary is rounded through bf16 the way the GPU path stores it
-    (used to separate rounding noise from real error)."""
-    rb = (lambda t: round_bf16(t)) if round_boundaries else (lambda t: t)
+    tensor/src/activation.rs:309-318).  Evaluated in f32 on bf16-rounded x and weights.
+
+    round_boundaries selects where intermediate results pass through bf16:
+      False       nowhere (the pure-f32 oracle the headline tolerance is stated against);
+      True/"ops"  after every op, as the dtypes of the reference's bf16 graph dictate (matmul casts its f32 sum back
+                  to bf16, tensor/src/reduce.rs:673-691, before a residual add or the gate sees it);
+      "kernels"   only where a kernel of the fused schedule stores a result: the residual add of `h + a @ Wo` /
+                  `h + ff @ Wdown` and the gate `silu(x @ Wgate) * (x @ Wup)` consume the f32 sums of their matmuls,
+                  which is what a kernel that keeps those ops together (the reference counts them as one kernel,
+                  tensor/src/test/unit/fusion.rs:21-33,58-67) has in its registers."""
+    mode = {False: "none", True: "ops", None: "none"}.get(round_boundaries, round_boundaries)
+    if mode not in ("none", "ops", "kernels"):
+        raise ValueError(f"round_boundaries: {round_boundaries!r}")
+    rb = (lambda t: t) if mode == "none" else (lambda t: round_bf16(t))          # a stored result
+    rb_op = (lambda t: round_bf16(t)) if mode == "ops" else (lambda t: t)        # a result that a fused kernel keeps in f32
     hidden = x_bits.shape[-1]
     T = batch * seq
     h = bf16_to_f32(x_bits).reshape(T, hidden)
@@ -379,8 +392,8 @@ def decoder_layer_f32(x_bits, w, batch, seq, n_q, n_kv, head_dim, eps=1e-5, thet
     qh, kh, vh = (np.ascontiguousarray(t.transpose(0, 2, 1, 3)) for t in (q, k, v))
     a = rb(sdpa_f32(qh, kh, vh, causal=True))
     a = np.ascontiguousarray(a.transpose(0, 2, 1, 3)).reshape(T, n_q * head_dim)
-    h = rb(h + rb(matmul_f32(a, W["wo"])))
+    h = rb(h + rb_op(matmul_f32(a, W["wo"])))
     n2 = rb(rms_norm_f32(h, eps, g2))
-    ff = rb(swiglu_f32(rb(matmul_f32(n2, W["wgate"])), rb(matmul_f32(n2, W["wup"]))))
-    out = rb(h + rb(matmul_f32(ff, W["wdown"])))
+    ff = rb(swiglu_f32(rb_op(matmul_f32(n2, W["wgate"])), rb_op(matmul_f32(n2, W["wup"]))))
+    out = rb(h + rb_op(matmul_f32(ff, W["wdown"])))
     return out.reshape(batch, seq, hidden)

@@ -26,7 +26,7 @@ def test_header_symbols_exported_and_bound():
         assert hasattr(lib, n), f"{n} declared in the header but not exported"
         assert n in _ffi.PROTOTYPES, f"{n} has no ctypes prototype"
     assert set(_ffi.PROTOTYPES) <= set(names), set(_ffi.PROTOTYPES) - set(names)
-    assert lib.mk_abi_version() == 3
+    assert lib.mk_abi_version() == 4
 
 
 def test_struct_layouts_match_header():

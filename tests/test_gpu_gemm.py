@@ -153,20 +153,73 @@ def test_config2_full_size_sampled_rows_and_linearity(dev):
     b_bits = orc.normal_bf16(rng, (K, N), 0.02)
     A, B = dev.from_numpy(a_bits), dev.from_numpy(b_bits)
     Cb = dev.alloc(M * N * 2)
+    fill_poison(dev, Cb, M * N * 2)
     dev.gemm(A, B, Cb, M, N, K, mk.MK_BF16)
     assert dev.kernel_status() == 0
     c = Cb.copyout(np.uint16, (M, N))
-    rows = np.array([0, 1, 127, 128, 129, 4095, 4096, 8063, 8064, 8190, 8191] + list(rng.integers(0, M, 21)))
+    rows = np.array([0, 1, 127, 128, 129, 255, 256, 4095, 4096, 8063, 8064, 8190, 8191] + list(rng.integers(0, M, 21)))
     ref = orc.matmul_f32(orc.bf16_to_f32(a_bits[rows]), orc.bf16_to_f32(b_bits))
     assert_close(orc.bf16_to_f32(c[rows]), ref, mk.MK_BF16, "config 2 sampled rows")
-    # every tile was written: no element kept the poison pattern
+    # every tile was written: C was filled with 0xFFFF (a NaN pattern) before the launch and no element kept it
     assert not np.any(c == 0xFFFF)
     # column checksum: sum over all rows of C equals (sum over rows of A) @ B within accumulated rounding
-    colsum = orc.bf16_to_f32(c).astype(np.float64).sum(axis=0)
-    ref_colsum = orc.bf16_to_f32(a_bits).astype(np.float64).sum(axis=0) @ orc.bf16_to_f32(b_bits).astype(np.float64)
+    colsum, ref_colsum = column_checksums(c, a_bits, b_bits)
     assert np.max(np.abs(colsum - ref_colsum)) < 0.02 * np.sqrt(M) + 2e-2 * np.max(np.abs(ref_colsum))
     for x in (A, B, Cb):
         x.free()
+
+
+def fill_poison(dev, buf, nbytes):
+    """0xFF in every byte of the buffer: a bf16 NaN pattern that no finished output element keeps."""
+    _ffi.check(dev.lib.mk_memset_async(dev.h, buf.ptr, 0xFF, nbytes, None))
+    dev.sync()
+
+
+def column_checksums(c_bits, a_bits, b_bits, block=1024):
+    """(sum over rows of C, (sum over rows of A) @ B), both in float64, evaluated block-wise to bound host memory."""
+    M, N = c_bits.shape
+    colsum = np.zeros(N, np.float64)
+    for r in range(0, M, block):
+        colsum += orc.bf16_to_f32(c_bits[r:r + block]).astype(np.float64).sum(axis=0)
+    a_sum = np.zeros(a_bits.shape[1], np.float64)
+    for r in range(0, M, block):
+        a_sum += orc.bf16_to_f32(a_bits[r:r + block]).astype(np.float64).sum(axis=0)
+    ref = np.zeros(N, np.float64)
+    for k in range(0, a_bits.shape[1], block):
+        ref += a_sum[k:k + block] @ orc.bf16_to_f32(b_bits[k:k + block]).astype(np.float64)
+    return colsum, ref
+
+
+def test_config5_full_size_sampled_rows_tile_seams_and_checksum(dev):
+    """The sharded sweep's GEMM on one GPU: bf16 M=16384 K=8192 N=28672 (f32 accumulate, bf16 out).  32+ rows --
+    first and last rows of 256-row tiles, the seams between tiles, random rows -- against the oracle; every
+    element overwritten (0xFFFF poison); column checksum over the whole matrix."""
+    M, K, N = 16384, 8192, 28672
+    rng = np.random.default_rng(5)
+    a_bits = orc.normal_bf16(rng, (M, K), 1.0)
+    b_bits = orc.normal_bf16(rng, (K, N), 0.02)
+    A, B = dev.from_numpy(a_bits), dev.from_numpy(b_bits)
+    Cb = dev.alloc(M * N * 2)
+    fill_poison(dev, Cb, M * N * 2)
+    before = dev.launch_count()
+    dev.gemm(A, B, Cb, M, N, K, mk.MK_BF16)
+    assert dev.kernel_status() == 0
+    assert dev.launch_count() - before == 1
+    c = Cb.copyout(np.uint16, (M, N))
+    seams = [0, 1, 127, 128, 255, 256, 257, 511, 512, 8191, 8192, 8447, 8448, 16127, 16128, 16255, 16256, 16382, 16383]
+    rows = np.array(seams + list(rng.integers(0, M, 16)))
+    assert len(rows) >= 32
+    ref = orc.matmul_f32(orc.bf16_to_f32(a_bits[rows]), orc.bf16_to_f32(b_bits))
+    got = orc.bf16_to_f32(c[rows])
+    assert_close(got, ref, mk.MK_BF16, "config 5 GEMM sampled rows")
+    rel_rms = float(np.sqrt(np.mean((got - ref) ** 2)) / np.sqrt(np.mean(ref ** 2)))
+    assert rel_rms < 5e-3, f"relative rms error {rel_rms:.3e}"
+    assert not np.any(c == 0xFFFF), "some output element was never written"
+    colsum, ref_colsum = column_checksums(c, a_bits, b_bits)
+    assert np.max(np.abs(colsum - ref_colsum)) < 0.03 * np.sqrt(M) + 2e-2 * np.max(np.abs(ref_colsum))
+    for x in (A, B, Cb):
+        x.free()
+    dev.trim()
 
 
 # ---------------------------------------------------------------------------------------------

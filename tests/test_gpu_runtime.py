@@ -282,3 +282,90 @@ def test_threads_with_their_own_streams_share_one_device(dev):
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_attention_claim_counters_are_per_stream_and_per_plan(dev):
+    """The persistent attention kernel claims work items from a counter.  A recorded plan keeps its counter for
+    life and every stream has its own, so a plan replaying on one stream while hundreds of eager attention calls
+    run on another never consume each other's claims: both outputs still match the oracle."""
+    from morok_b200 import Tensor
+    B, H, S, D = 1, 8, 1024, 128
+    rng = np.random.default_rng(77)
+    q1, k1, v1 = (orc.normal_bf16(rng, (B, H, S, D)) for _ in range(3))
+    q2, k2, v2 = (orc.normal_bf16(rng, (B, H, S, D)) for _ in range(3))
+    bf = orc.bf16_to_f32
+    ref1 = orc.sdpa_f32(bf(q1), bf(k1), bf(v1), causal=True)
+    ref2 = orc.sdpa_f32(bf(q2), bf(k2), bf(v2), causal=True)
+    plan = Tensor.from_ndarray(dev, q1).scaled_dot_product_attention(Tensor.from_ndarray(dev, k1), Tensor.from_ndarray(dev, v1),
+                                                                       is_causal=True).compile()
+    Q2, K2, V2 = dev.from_numpy(q2), dev.from_numpy(k2), dev.from_numpy(v2)
+    O2 = dev.alloc(B * H * S * D * 2)
+    s_plan = mk.Stream(dev)
+    for i in range(300):                    # more launches than there are counter slots
+        plan.launch(s_plan)
+        dev.sdpa(Q2, K2, V2, O2, B, H, H, S, S, D, dtype=mk.MK_BF16, causal=True)
+    assert dev.kernel_status(s_plan) == 0
+    assert dev.kernel_status() == 0
+    assert_close(bf(plan.result.as_ndarray()), ref1, mk.MK_BF16, "attention replayed from a plan beside eager launches")
+    assert_close(bf(O2.copyout(np.uint16, (B, H, S, D))), ref2, mk.MK_BF16, "eager attention beside a replaying plan")
+    plan.free()
+    s_plan.close()
+
+
+def test_cached_block_is_not_reused_under_a_running_kernel(dev):
+    """Reuse out of the allocator cache is ordered after the work that was in flight when the block was freed:
+    A is freed while GEMMs that read it are still queued on stream 1, the next allocation of that size gets the
+    same block back and is overwritten through stream 2 -- and the GEMM result is still that of the old contents."""
+    M, K, N = 4096, 4096, 4096
+    rng = np.random.default_rng(3)
+    a = orc.normal_bf16(rng, (M, K), 1.0)
+    b = orc.normal_bf16(rng, (K, N), 0.02)
+    dev.trim()
+    s1, s2 = mk.Stream(dev), mk.Stream(dev)
+    A, Bw, Cb = dev.from_numpy(a), dev.from_numpy(b), dev.alloc(M * N * 2)
+    dev.sync()
+    a_ptr = A.ptr
+    for _ in range(40):                         # tens of milliseconds of queued work that reads A
+        dev.gemm(A, Bw, Cb, M, N, K, mk.MK_BF16, stream=s1)
+    A.free()                                    # no sync: the allocator has to order the reuse itself
+    X = dev.alloc(M * K * 2)
+    assert X.ptr == a_ptr                       # the same block, straight from the cache
+    X.copyin(np.full((M, K), 0x7FC0, np.uint16), stream=s2)      # NaNs over the old A, on another stream
+    s1.sync()
+    s2.sync()
+    assert dev.kernel_status(s1) == 0
+    rows = np.array([0, 1, 2047, 4095])
+    got = orc.bf16_to_f32(Cb.copyout(np.uint16, (M, N))[rows])
+    ref = orc.matmul_f32(orc.bf16_to_f32(a[rows]), orc.bf16_to_f32(b))
+    assert_close(got, ref, mk.MK_BF16, "GEMM whose input block was freed and reused while it was queued")
+    for x in (X, Bw, Cb):
+        x.free()
+    s1.close()
+    s2.close()
+
+
+def test_recorded_tensor_holds_no_data_until_its_plan_has_run(dev):
+    from morok_b200 import Tensor
+    rng = np.random.default_rng(5)
+    a_bits, b_bits = orc.normal_bf16(rng, (64, 64), 1.0), orc.normal_bf16(rng, (64, 64), 1.0)
+    a, b = Tensor.from_ndarray(dev, a_bits), Tensor.from_ndarray(dev, b_bits)
+    c = a.matmul(b)
+    plan = c.compile()
+    with pytest.raises(mk.MorokError) as e:     # recorded, never launched: nothing to read yet
+        c.as_ndarray()
+    assert e.value.status == _ffi.MK_ERR_NOT_ALLOCATED
+    with pytest.raises(mk.MorokError) as e:     # ... and nothing an eager graph could consume
+        c.matmul(b).realize()
+    assert e.value.status == _ffi.MK_ERR_NOT_ALLOCATED
+    # the plan keeps the leaf buffers it reads: dropping the input tensors and recycling memory of their size
+    # must not reach the plan's data
+    del a, b
+    junk = [dev.from_numpy(np.full((64, 64), 0x7FC0, np.uint16)) for _ in range(4)]
+    plan.launch()
+    dev.sync()
+    assert dev.kernel_status() == 0
+    got = orc.bf16_to_f32(c.as_ndarray())
+    assert_close(got, orc.matmul_f32(orc.bf16_to_f32(a_bits), orc.bf16_to_f32(b_bits)), mk.MK_BF16, "plan replay after its inputs were dropped")
+    for j in junk:
+        j.free()
+    plan.free()

@@ -228,19 +228,36 @@ def test_config4_full_size_layer_causal_prefix_vs_oracle(dev):
     assert out.last_launches() == 11
     got = orc.bf16_to_f32(out.as_ndarray()).reshape(batch, seq, hidden)
     assert np.all(np.isfinite(got))
-    # Eleven kernels with bf16 results in a row, the last one summing 14336 products of bf16-rounded activations:
-    # rounding noise at the op boundaries (|gate|, |up| reach 6, so one bf16 ulp is 0.03) compounds
-    # to ~1e-2 rms at the output whatever the implementation, so the per-op element-wise bar
-    # (1e-2 + 2e-2|ref|) cannot apply to the chain.  The chain is held to normalised bounds against
-    # the pure-f32 oracle instead; every op on its own meets the per-op bar (tests above).
+    # Three oracles.  (1) "kernels": f32 arithmetic, results rounded through bf16 exactly where a kernel of the fused
+    # schedule stores one (norm, each projection, RoPE, attention, residual sums, the gated product) -- the arithmetic
+    # this path implements; the layer is held to the element-wise bar of the bf16 paths (2e-2 relative + 1e-2
+    # absolute) against it.  (2) "ops": rounded after every op, what the dtypes of the reference's bf16 graph dictate
+    # (tensor/src/reduce.rs:673-691).  (3) pure f32 on the bf16-rounded inputs.  Eleven bf16 results in a row, the last
+    # one a sum of 14336 products of rounded activations, put ~1.4e-2 of absolute rounding noise on the output whatever
+    # the implementation: oracles (1) and (2) themselves disagree beyond the element-wise bar on ~4 % of the
+    # elements (small outputs, where the bar is 1e-2), so against (2) and (3) the layer is bounded in relative rms and
+    # must be no further from (3) than (2) is.
     for b, prefix in ((0, 160), (7, 96)):
-        ref = orc.decoder_layer_f32(x[b:b + 1, :prefix], w, 1, prefix, n_q, n_kv, hd)
-        err = np.abs(got[b:b + 1, :prefix] - ref)
-        rms_rel = float(np.sqrt(np.mean(err ** 2)) / np.sqrt(np.mean(ref ** 2)))
-        max_norm = float(err.max() / np.abs(ref).max())
-        assert rms_rel < 1e-2 and max_norm < 2e-2, f"config 4, batch element {b}: rms rel {rms_rel:.3e}, normalised max {max_norm:.3e}"
-        within = np.mean(err <= 1e-2 + 2e-2 * np.abs(ref))
-        assert within > 0.85, f"only {within:.3f} of the elements within the per-op bar"
+        xs = x[b:b + 1, :prefix]
+        ref_k = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd, round_boundaries="kernels")
+        g = got[b:b + 1, :prefix]
+        err = np.abs(g - ref_k)
+        bad = err > 1e-2 + 2e-2 * np.abs(ref_k)
+        assert not bad.any(), (f"config 4, batch element {b}: {int(bad.sum())}/{bad.size} elements beyond 2e-2 rel / 1e-2 abs of the "
+                               f"kernel-boundary oracle; max err {float(err.max()):.4g}, rms {float(np.sqrt(np.mean(err ** 2))):.3e}")
+        ref = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd)
+        ref_o = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd, round_boundaries="ops")
+        scale = float(np.sqrt(np.mean(ref ** 2)))
+
+        def rms_rel(a, r):
+            return float(np.sqrt(np.mean((a - r) ** 2))) / scale
+        d_f32, d_ops, ops_f32 = rms_rel(g, ref), rms_rel(g, ref_o), rms_rel(ref_o, ref)
+        max_norm = float(np.abs(g - ref).max() / np.abs(ref).max())
+        print(f"config 4 batch element {b}: rms rel vs pure-f32 oracle {d_f32:.3e} (normalised max {max_norm:.3e}), vs per-op "
+              f"bf16 oracle {d_ops:.3e}; per-op bf16 oracle vs pure-f32 oracle {ops_f32:.3e}; vs kernel-boundary oracle {rms_rel(g, ref_k):.3e}")
+        assert d_f32 < 1e-2 and max_norm < 2e-2, f"config 4, batch element {b}: rms rel {d_f32:.3e}, normalised max {max_norm:.3e}"
+        assert d_f32 <= ops_f32 * 1.05 + 1e-4, f"further from the f32 oracle ({d_f32:.3e}) than the reference's own bf16 graph is ({ops_f32:.3e})"
+        assert d_ops < 1e-2
     # batch elements are independent: identical inputs give identical outputs
     x2 = x.copy()
     x2[3] = x2[5]
