@@ -189,7 +189,8 @@ def run_ours(args, rank, world, local_rank, dist):
     def tensor(shape, sigma, seed, keep):
         n = int(np.prod(shape))
         buf = dev.alloc(n * 2)
-        host = synth.fill_normal_bf16(dev, buf, n, sigma, seed, keep_host=keep)
+        # a development run that skips the delivery check repeats one random chunk instead of drawing every element
+        host = synth.fill_normal_bf16(dev, buf, n, sigma, seed, keep_host=keep, tile=(world > 1 and not check))
         return buf, (host.reshape(shape) if host is not None else None)
 
     A, A_host = tensor((M, K), 1.0, 1, check)

@@ -547,6 +547,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Tensor maps of the output as every destination sees it: [0] the local C, [1 ..] the peers' C (16-bit elements,
+// box of 64 columns x 32 rows, 128-byte swizzle).
+struct CStoreMaps {
+    CUtensorMap m[1 + MK_MAX_PEERS];
+};
+
+// Epilogue of one 128 x 256 accumulator for N-sharded runs: the warp turns its 32 rows into 16-bit output, 64
+// columns at a time, in the shared-memory layout of a 128-byte-swizzled tile store, and one lane hands each
+// 32 x 64 block to the copy engine of the SM once per destination (local C and every peer's C over NVLink).
+// The stores are asynchronous: the warp goes on draining while they travel, and only waits before it rewrites a
+// block that may still be read (each of the four blocks of a tile is one bulk group, the four newest may be
+// pending).  `stage` is this warp's 16 KiB (4 blocks of 32 rows x 128 bytes).
+template <int OUT>
+__device__ __forceinline__ void epilogue_tile_tma(const TcParams& p, const CStoreMaps& maps, int64_t tile_row0, int64_t col0, uint32_t taddr,
+                                                  uint8_t* stage, int q, int lane, uint32_t tempty_bar, bool tempty_remote) {
+    static_assert(OUT != MK_F32, "tile stores carry 16-bit outputs");
+    const int64_t row0 = tile_row0 + q * 32;
+    const int64_t row = row0 + lane;
+    const int nslabs = (int)min((int64_t)(BN / 64), (p.N - col0 + 63) / 64);      // 64-column blocks of this tile inside N (>= 1)
+#pragma unroll 1
+    for (int sl = 0; sl < nslabs; ++sl) {
+        uint8_t* blk = stage + sl * 4096;
+        if (lane == 0) bulk_wait_group_read<3>();       // the store that last read this block (previous tile) is done with it
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + sl * 64 + c * 32, r);
+            tmem_wait_ld();
+            uint32_t w[16];
+            convert_chunk<OUT>(p, row, col0 + sl * 64 + c * 32, r, w);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                *reinterpret_cast<uint4*>(blk + lane * 128 + (((c * 4 + i) ^ (lane & 7)) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+        if (sl == nslabs - 1) {     // last read of this accumulator: hand it back before the stores are issued
+            tc_fence_before();
+            arrive_tempty(tempty_bar, tempty_remote);
+        }
+        fence_proxy_async_smem();   // this lane's shared-memory writes become visible to the copy engine
+        __syncwarp();
+        if (lane == 0) {
+            if (row0 < p.M) {
+                const uint32_t src = smem_u32(blk);
+                const int x = (int)(col0 + sl * 64), y = (int)row0;
+                for (int d = 0; d <= p.n_peers; ++d) tma_store_2d(&maps.m[d], src, x, y);
+            }
+            bulk_commit_group();
+        }
+    }
+    // fewer than four blocks in this tile (ragged N): keep the group count per tile at four so that the wait above stays exact
+    if (lane == 0)
+        for (int sl = nslabs; sl < BN / 64; ++sl) bulk_commit_group();
+}
+
 // ---------------------------------------------------------------------------------------------------
 // CTA-pair variant: two CTAs of a cluster (one per SM) share each MMA (cta_group::2).  The pair owns a
 // 256 x 256 tile; CTA r loads rows r*128.. of A and columns r*128.. of B of every k-block (its own
@@ -561,17 +616,26 @@ constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = BM * BK * 2;             // 16 KiB: this CTA's 128 rows of A
 constexpr int P_B_BYTES = BK * (BN / 2) * 2;       // 16 KiB: this CTA's 128 columns of B
 constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr int P_NUM_BARS = 2 * P_STAGES + 4;
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + OUT_STAGE_BYTES + 1024 + 256;
 
-template <bool TRANS_B, int OUT, bool F8 = false>
+// Shared memory of the pair kernel: NSTG ring stages, the output staging, barriers.  With tile-store delivery
+// (TMA_OUT) the staging holds a whole 128 x 256 tile of 16-bit output (64 KiB) and the ring is one stage shorter.
+template <bool TMA_OUT>
+struct PairCfg {
+    static constexpr int NSTG = TMA_OUT ? P_STAGES - 1 : P_STAGES;
+    static constexpr int OUT_BYTES = TMA_OUT ? 4 * 16384 : OUT_STAGE_BYTES;
+    static constexpr int NUM_BARS = 2 * NSTG + 4;
+    static constexpr int SMEM_BYTES = NSTG * P_STAGE_BYTES + OUT_BYTES + 1024 + 256;
+};
+
+template <bool TRANS_B, int OUT, bool F8 = false, bool TMA_OUT = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
-                    const TcParams p) {
+                    const TcParams p, const __grid_constant__ CStoreMaps cmaps) {
+    constexpr int P_STAGES = PairCfg<TMA_OUT>::NSTG, P_NUM_BARS = PairCfg<TMA_OUT>::NUM_BARS;     // shadow the file-level defaults
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stage_out = smem + P_STAGES * P_STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + OUT_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stage_out + PairCfg<TMA_OUT>::OUT_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + P_NUM_BARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -598,6 +662,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         prefetch_tensormap(&tmA);
         prefetch_tensormap(&tmB);
         prefetch_tensormap(&tmB2);
+        if constexpr (TMA_OUT)
+            for (int d = 0; d <= p.n_peers; ++d) prefetch_tensormap(&cmaps.m[d]);
     }
     if (warp == 2) {   // the same warp of both CTAs allocates the pair's tensor memory
         tmem_alloc_pair(smem_u32(tmem_slot), TMEM_COLS);
@@ -694,10 +760,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const bool ready = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.kerr, KERR_GEMM_EPILOGUE_WAIT, t);
             if (!__all_sync(0xffffffffu, ready)) break;
             tc_fence_after();
-            epilogue_tile<OUT>(p, (int64_t)tm * (2 * BM) + (int64_t)rank * BM, (int64_t)tn * (p.dual ? BN / 2 : BN),
-                               tmem_base + (uint32_t(q * 32) << 16) + acc * BN, stage_out, q, lane, leader_tempty + 8 * acc, true);
+            if constexpr (TMA_OUT)
+                epilogue_tile_tma<OUT>(p, cmaps, (int64_t)tm * (2 * BM) + (int64_t)rank * BM, (int64_t)tn * BN,
+                                       tmem_base + (uint32_t(q * 32) << 16) + acc * BN, stage_out + q * 16384, q, lane, leader_tempty + 8 * acc, true);
+            else
+                epilogue_tile<OUT>(p, (int64_t)tm * (2 * BM) + (int64_t)rank * BM, (int64_t)tn * (p.dual ? BN / 2 : BN),
+                                   tmem_base + (uint32_t(q * 32) << 16) + acc * BN, stage_out, q, lane, leader_tempty + 8 * acc, true);
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
+        }
+        if constexpr (TMA_OUT) {
+            if (lane == 0) bulk_wait_group<0>();     // every tile store of this warp has completed before the CTA may leave
+            __syncwarp();
         }
     }
 
@@ -813,15 +887,41 @@ mk_status launch_tc(mk_device* dev, cudaStream_t st, const CUtensorMap& ta, cons
 
 template <bool TRANS_B, int OUT, bool F8 = false>
 mk_status launch_tc_pair(mk_device* dev, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const TcParams& p) {
-    auto kern = gemm_tc_pair_kernel<TRANS_B, OUT, F8>;
-    MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+    auto kern = gemm_tc_pair_kernel<TRANS_B, OUT, F8, false>;
+    MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false>::SMEM_BYTES));
     const int tiles = p.tiles_m2 * p.tiles_n;
     const int clusters = tiles < dev->prop.multiProcessorCount / 2 ? tiles : dev->prop.multiProcessorCount / 2;
-    kern<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(ta, tb, tb2, p);
+    static const CStoreMaps no_maps{};      // read by the tile-store variant only
+    kern<<<2 * clusters, NUM_THREADS, PairCfg<false>::SMEM_BYTES, st>>>(ta, tb, tb2, p, no_maps);
     MK_CUDA(cudaGetLastError());
     note_launch(dev, st, p.dual ? "gemm_tc_pair_gated" : (F8 ? "gemm_tc_pair_f8" : "gemm_tc_pair"));
     return MK_OK;
 }
+
+// The same kernel with the epilogue that delivers finished tiles by tile stores (N-sharded runs, 16-bit output).
+template <bool TRANS_B, int OUT>
+mk_status launch_tc_pair_deliver(mk_device* dev, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p, const CStoreMaps& maps) {
+    auto kern = gemm_tc_pair_kernel<TRANS_B, OUT, false, true>;
+    constexpr int smem = PairCfg<true>::SMEM_BYTES;
+    MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int tiles = p.tiles_m2 * p.tiles_n;
+    const int clusters = tiles < dev->prop.multiProcessorCount / 2 ? tiles : dev->prop.multiProcessorCount / 2;
+    kern<<<2 * clusters, NUM_THREADS, smem, st>>>(ta, tb, tb, p, maps);
+    MK_CUDA(cudaGetLastError());
+    note_launch(dev, st, "gemm_tc_pair_deliver");
+    return MK_OK;
+}
+
+// Peers receive their copies as tile stores issued from shared memory (MOROK_B200_PEER_TMA=0: as 16-byte stores of
+// the epilogue warps, the older path).
+bool peer_tma_enabled() {
+    static int v = [] {
+        const char* e = getenv("MOROK_B200_PEER_TMA");
+        return e ? atoi(e) : 1;
+    }();
+    return v != 0;
+}
+
 
 // K ranges for few-row problems (MOROK_B200_GEMM_SPLITK=0/1 forces).
 bool split_k_enabled() {
@@ -978,6 +1078,20 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
             continue;
         }
 
+        // N-sharded delivery: 16-bit tiles leave through tile stores, one per destination
+        if (pair && !dual && !f8 && d.n_peers > 0 && d.dtype_out != MK_F32 && p.staged && peer_tma_enabled()) {
+            alignas(64) CStoreMaps maps;
+            mk_status sm = MK_OK;
+            for (int q = 0; q <= d.n_peers && sm == MK_OK; ++q)
+                sm = encode_2d(&maps.m[q], d.dtype_out, q == 0 ? p.C : p.peer_C[q - 1], (uint64_t)d.N, (uint64_t)d.M, (uint64_t)d.ldc * 2, 64, 32);
+            if (sm != MK_OK) return sm;
+            mk_status sd;
+            if (d.trans_b) sd = d.dtype_out == MK_BF16 ? launch_tc_pair_deliver<true, MK_BF16>(dev, st, ta, tb, p, maps) : launch_tc_pair_deliver<true, MK_F16>(dev, st, ta, tb, p, maps);
+            else sd = d.dtype_out == MK_BF16 ? launch_tc_pair_deliver<false, MK_BF16>(dev, st, ta, tb, p, maps) : launch_tc_pair_deliver<false, MK_F16>(dev, st, ta, tb, p, maps);
+            if (sd != MK_OK) return sd;
+            continue;
+        }
+
         mk_status s2;
 #define MK_TC(TB, OUT) s2 = pair ? launch_tc_pair<TB, OUT>(dev, st, ta, tb, tb2, p) : launch_tc<TB, OUT>(dev, st, ta, tb, p)
 #define MK_TC8(OUT) s2 = pair ? launch_tc_pair<true, OUT, true>(dev, st, ta, tb, tb2, p) : launch_tc<true, OUT, true>(dev, st, ta, tb, p)
@@ -1039,11 +1153,12 @@ mk_status static_setup(int ordinal) {
 template <bool TRANS_B, int OUT>
 mk_status launch_tc_static(int sms, bool pair, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const TcParams& p) {
     if (pair) {
-        auto kern = gemm_tc_pair_kernel<TRANS_B, OUT>;
-        MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+        auto kern = gemm_tc_pair_kernel<TRANS_B, OUT, false, false>;
+        MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<false>::SMEM_BYTES));
         const int tiles = p.tiles_m2 * p.tiles_n;
         const int clusters = tiles < sms / 2 ? tiles : sms / 2;
-        kern<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(ta, tb, tb, p);
+        static const CStoreMaps no_maps{};
+        kern<<<2 * clusters, NUM_THREADS, PairCfg<false>::SMEM_BYTES, st>>>(ta, tb, tb, p, no_maps);
     } else {
         auto kern = gemm_tc_kernel<TRANS_B, OUT>;
         MK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));

@@ -58,6 +58,7 @@ enum : unsigned int {
     KERR_SDPA_PRODUCER_WAIT = 0x201,
     KERR_SDPA_MMA_WAIT = 0x202,
     KERR_SDPA_SOFTMAX_WAIT = 0x203,
+    KERR_SDPA_STORE_WAIT = 0x204,
     KERR_SKINNY_PRODUCER_WAIT = 0x301,
     KERR_SKINNY_CONSUMER_WAIT = 0x302,
     KERR_SKINNY_REDUCE_WAIT = 0x303,

@@ -104,6 +104,32 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// Tile stores, shared memory -> global (the destination may be a peer GPU's memory mapped into this process):
+// asynchronous, tracked per issuing thread in bulk groups.  The source must have been made visible to the async
+// proxy (fence_proxy_async_smem) and must stay untouched until bulk_wait_group_read lets the group go.
+// Elements outside the tensor map's extents are not written.  x * element size must be a multiple of 16 bytes
+// and no coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int x, int y, int z, int w) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap), "r"(src_smem), "r"(x),
+                 "r"(y), "r"(z), "r"(w)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once all but the newest N bulk groups of this thread have finished READING their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Returns once all but the newest N bulk groups of this thread have completed (their writes are performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---- tensor memory (TMEM) ------------------------------------------------------------------------------
 // Executed by one full warp.  ncols: power of two in [32, 512].  The base address lands in *dst_smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {

@@ -45,8 +45,15 @@ struct Cfg {
     static constexpr int SMEM_Q = 2 * TILE_BYTES;
     static constexpr int SMEM_K = KV_STAGES * TILE_BYTES;
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4;
+    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 2;
     static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + 1024 + 256;
+    // head-sharded runs that deliver O by tile stores stage one 128-row tile of output beside the operands
+    static constexpr int SMEM_BYTES_DELIVER = SMEM_BYTES + TILE_BYTES;
+};
+// Tensor maps of the output as every destination sees it: [0] the local O, [1 ..] the peers' O
+// ([B, H, S, D] with the caller's strides; box of 64 columns x 128 rows, 128-byte swizzle).
+struct OStoreMaps {
+    CUtensorMap m[1 + MK_MAX_PEERS];
 };
 constexpr int NUM_THREADS = 352;        // 11 warps
 constexpr int TMEM_COLS = 512;
@@ -65,6 +72,7 @@ struct FaParams {
     int q_pairs;        // ceil(Sq / 256)
     unsigned int* work_counter;   // device-wide claim counter, zeroed before the launch
     int stage_o;        // stage O through shared memory for coalesced stores (always when peers receive copies)
+    int tma_o;          // ... in a staging tile of its own, from which warp 10 issues one tile store per destination
     int n_peers;
     void* peer_O[MK_MAX_PEERS];
     KernelError* kerr;
@@ -205,14 +213,15 @@ __device__ __forceinline__ WorkItem decode_item(const FaParams& p, int idx) {
 template <bool BF16, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-               const FaParams p) {
+               const FaParams p, const __grid_constant__ OStoreMaps omaps) {
     constexpr int TILE_BYTES = Cfg<HD>::TILE_BYTES, HALF_BYTES = Cfg<HD>::HALF_BYTES, KV_STAGES = Cfg<HD>::KV_STAGES;
     constexpr int SMEM_Q = Cfg<HD>::SMEM_Q, SMEM_K = Cfg<HD>::SMEM_K, SMEM_V = Cfg<HD>::SMEM_V, NUM_BARS = Cfg<HD>::NUM_BARS;
     constexpr int NH = HD / 64;      // 64-column boxes per tile
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sQ = smem_u32(smem), sK = sQ + SMEM_Q, sV = sK + SMEM_K;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_Q + SMEM_K + SMEM_V);
+    uint8_t* stageO = smem + SMEM_Q + SMEM_K + SMEM_V;      // present only when p.tma_o (the launch then asks for TILE_BYTES more)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_Q + SMEM_K + SMEM_V + (p.tma_o ? TILE_BYTES : 0));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -226,6 +235,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bar_ofree = bar_qempty + 8;               // [2] O_t drained by the epilogue of the previous item
     const uint32_t bar_ifull = bar_ofree + 16;               // [2] work-item slot published by the producer
     const uint32_t bar_iempty = bar_ifull + 16;              // [2] work-item slot read by every consumer
+    const uint32_t bar_ostage_full = bar_iempty + 16;        // output staging tile written by the four warps of a query tile
+    const uint32_t bar_ostage_free = bar_ostage_full + 8;    // ... and read out by the tile stores warp 10 issued
     volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2] claimed item indices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -235,7 +246,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mbar_init(bar_q, 1);
         // Q tiles are free once the item's last S MMA retired (one commit); when the output is staged in
         // the Q tiles, also once every softmax warp has read its staged rows back (one lane each).
-        mbar_init(bar_qempty, p.stage_o ? 1 + 8 : 1);
+        mbar_init(bar_qempty, (p.stage_o && !p.tma_o) ? 1 + 8 : 1);
+        mbar_init(bar_ostage_full, 128);
+        mbar_init(bar_ostage_free, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(bar_kfull + 8 * i, 1);
             mbar_init(bar_kempty + 8 * i, 1);
@@ -248,13 +261,15 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_init(bar_pvdone + 8 * t, 1);
             mbar_init(bar_ofree + 8 * t, 4);   // one lane per softmax warp of the tile
             mbar_init(bar_ifull + 8 * t, 1);
-            mbar_init(bar_iempty + 8 * t, 1 + 8);
+            mbar_init(bar_iempty + 8 * t, 1 + 8 + (p.tma_o ? 1 : 0));    // MMA warp, eight softmax warps, and the store warp when it takes part
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
+        if (p.tma_o)
+            for (int d = 0; d <= p.n_peers; ++d) prefetch_tensormap(&omaps.m[d]);
     }
     if (warp == 10) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -417,6 +432,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t tS = tmem_base + lane_base + t * 128;
         const uint32_t tO = tmem_base + lane_base + 256 + t * 128;
         uint32_t cum = 0;                        // key blocks of this tile processed in earlier items
+        uint32_t stage_uses = 0;                 // uses of the output staging tile in earlier items (tile-store delivery)
         bool ok = true;
       for (int n = 0; ok; ++n) {
         const int slot = n & 1;
@@ -535,7 +551,44 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : __int_as_float(0x7fc00000);
             const bool in_range = qrow < p.Sq;
-            if (p.stage_o) {
+            if (p.tma_o) {
+                // Head-sharded delivery: the normalised tile goes to the staging tile in the layout of a 128-byte-swizzled
+                // tile store (two boxes of 64 columns for 128-wide heads); warp 10 then issues one store per destination
+                // while these warps move on to their next item.  The staging tile serves both query tiles in turn:
+                // use u = uses of earlier items + (tile 1 after a tile 0 that had work).
+                const uint32_t u = stage_uses + ((t == 1 && w.nblk[0] > 0) ? 1u : 0u);
+                ok = mbar_wait(bar_ostage_free, (u & 1) ^ 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 900000 + n);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+    #pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(tO + c * 32, r);
+                        tmem_wait_ld();
+                        uint32_t pk[16];
+    #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
+                            if constexpr (BF16) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                            } else {
+                                __half2 h = __floats2half2_rn(a, b);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        }
+                        uint8_t* box = stageO + (c >> 1) * HALF_BYTES + row_in_tile * 128;     // 64-column box c / 2, this thread's row
+    #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<uint4*>(box + ((((c & 1) * 4 + i) ^ (row_in_tile & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    }
+                    tc_fence_before();
+                    fence_proxy_async_smem();           // the staged rows become visible to the copy engine
+                    mbar_arrive(bar_ostage_full);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
+                }
+            } else if (p.stage_o) {
                 // The Q tile's shared memory is free once the last MMA of this tile has retired: stage the
                 // normalised output there (16-byte pieces XOR-swizzled by row) so that the global stores
                 // -- local and to peer GPUs -- go out as whole rows (2 HD contiguous bytes) per group of lanes.
@@ -610,7 +663,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (p.lse && in_range)
                 p.lse[((int64_t)batch * p.Hq + head) * p.Sq + qrow] = (l > 0.0f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
-        if (p.stage_o) {            // the staging area (this item's Q tile) has been read back
+        stage_uses += (w.nblk[0] > 0 ? 1u : 0u) + (w.nblk[1] > 0 ? 1u : 0u);
+        if (p.stage_o && !p.tma_o) {            // the staging area (this item's Q tile) has been read back
             // A tile without work must not release the Q tiles of item n before item n-1's phase of the
             // barrier has completed; this item's Q having landed proves that it has.
             if (nblk == 0) {
@@ -622,6 +676,42 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         cum += nblk;
       }
+    }
+
+    else if (warp == 10 && p.tma_o) {
+        // ---------------------------------------------------------------- tile stores of finished output tiles
+        // Follows the work items like every other consumer; for each query tile that had work it waits until the four
+        // softmax warps have staged the tile, issues one tile store per 64-column box and destination (the local O and
+        // every peer's O over NVLink), and frees the staging tile once the copy engine has read it.
+        uint32_t u = 0;
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+            const int slot = n & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_ifull + 8 * slot, (n >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 500000 + n));
+            if (!ok) break;
+            const int idx = __reduce_max_sync(0xffffffffu, (int)item_slot[slot]);
+            if (lane == 0) mbar_arrive(bar_iempty + 8 * slot);
+            if (idx >= total_items) break;
+            const WorkItem w = decode_item(p, idx);
+            for (int t = 0; t < 2 && ok; ++t) {
+                if (w.nblk[t] == 0) continue;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_ostage_full, u & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, n));
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t src = smem_u32(stageO);
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+                        for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * HALF_BYTES, h * 64, w.q0 + t * BQ, w.head, w.batch);
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(bar_ostage_free);
+                }
+                __syncwarp();
+                ++u;
+            }
+        }
+        if (lane == 0) bulk_wait_group<0>();     // every tile store has completed before the CTA may leave
+        __syncwarp();
     }
 
     if (*abort_flag) __nanosleep(2000000);
@@ -696,6 +786,17 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     p.idesc_pv = idesc_f16(fmt, 0u, 1u, BQ, (uint32_t)d.D);
     p.q_pairs = (int)q_pairs;
     p.stage_o = d.n_peers > 0 || getenv("MOROK_B200_ATTN_STAGE_O") != nullptr;
+    // peers receive their copies as tile stores issued from a staging tile (MOROK_B200_PEER_TMA=0: as 16-byte stores
+    // of the softmax warps out of the item's Q tile, the older path)
+    static const bool peer_tma = [] { const char* e = getenv("MOROK_B200_PEER_TMA"); return e ? atoi(e) != 0 : true; }();
+    p.tma_o = (d.n_peers > 0 && peer_tma) || getenv("MOROK_B200_ATTN_TMA_O") != nullptr;
+    alignas(64) OStoreMaps omaps{};
+    if (p.tma_o) {
+        for (int i = 0; i <= d.n_peers; ++i) {
+            s1 = encode_bhsd(&omaps.m[i], d.dtype, i == 0 ? d.O : d.peer_O[i - 1], d.B, d.Hq, d.Sq, d.Dv, d.o_strides);
+            if (s1 != MK_OK) return s1;
+        }
+    }
     p.n_peers = d.n_peers;
     for (int i = 0; i < d.n_peers; ++i) p.peer_O[i] = d.peer_O[i];
     p.kerr = stream_kerr(dev, st);
@@ -708,12 +809,13 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     auto launch = [&](auto kernel, int smem_bytes) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
-        kernel<<<(unsigned)grid, NUM_THREADS, smem_bytes, st>>>(tq, tk, tv, p);
+        kernel<<<(unsigned)grid, NUM_THREADS, smem_bytes, st>>>(tq, tk, tv, p, omaps);
         return cudaSuccess;
     };
     const bool bf = d.dtype == MK_BF16;
-    if (d.D == 128) MK_CUDA(bf ? launch(sdpa_tc_kernel<true, 128>, Cfg<128>::SMEM_BYTES) : launch(sdpa_tc_kernel<false, 128>, Cfg<128>::SMEM_BYTES));
-    else MK_CUDA(bf ? launch(sdpa_tc_kernel<true, 64>, Cfg<64>::SMEM_BYTES) : launch(sdpa_tc_kernel<false, 64>, Cfg<64>::SMEM_BYTES));
+    const int smem128 = p.tma_o ? Cfg<128>::SMEM_BYTES_DELIVER : Cfg<128>::SMEM_BYTES, smem64 = p.tma_o ? Cfg<64>::SMEM_BYTES_DELIVER : Cfg<64>::SMEM_BYTES;
+    if (d.D == 128) MK_CUDA(bf ? launch(sdpa_tc_kernel<true, 128>, smem128) : launch(sdpa_tc_kernel<false, 128>, smem128));
+    else MK_CUDA(bf ? launch(sdpa_tc_kernel<true, 64>, smem64) : launch(sdpa_tc_kernel<false, 64>, smem64));
     MK_CUDA(cudaGetLastError());
     note_launch(dev, st, d.D == 128 ? "sdpa_tc_d128" : "sdpa_tc_d64");
     *handled = true;

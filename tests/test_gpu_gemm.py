@@ -515,3 +515,31 @@ def test_few_rows_with_strided_operands_and_batches(dev):
     for i in range(batch):
         assert_close(y[i, :, :N], orc.matmul_f32(a[i, :, :K], np.ascontiguousarray(w[i, :, :K].T)), mk.MK_BF16, f"batch {i}")
     assert np.all(np.isnan(y[:, :, N:]))
+
+
+def test_sharded_delivery_by_tile_stores_into_stand_in_peers(dev):
+    """The N-sharded form on one GPU: two more buffers of the same GPU stand in for the peers' C.  The CTA-pair kernel
+    must deliver every tile of its column block into all three matrices (tile stores: 32 x 64 boxes, rows and columns
+    ragged against them) and leave the other columns untouched."""
+    M, K, N, col0, ncols = 2040, 320, 5128, 2568, 2560          # this "rank" owns columns 2568 .. 5127 of a [M, 5128] matrix
+    rng = np.random.default_rng(21)
+    a, b = orc.normal_bf16(rng, (M, K), 1.0), orc.normal_bf16(rng, (K, N), 0.05)
+    A, B = dev.from_numpy(a), dev.from_numpy(b)
+    outs = [dev.from_numpy(np.full((M, N), 0xFFFF, np.uint16)) for _ in range(3)]
+    dev.profile_begin()
+    dev.gemm(A, B.view(col0 * 2, K * N * 2 - col0 * 2), outs[0], M, ncols, K, mk.MK_BF16, ldb=N, ldc=N,
+             c_ptr=outs[0].ptr + col0 * 2, peers=[o.ptr + col0 * 2 for o in outs[1:]])
+    launched = [name for name, _ in dev.profile_end()]
+    assert launched == ["gemm_tc_pair_deliver"], launched
+    assert dev.kernel_status() == 0
+    ref = orc.matmul_f32(orc.bf16_to_f32(a), orc.bf16_to_f32(b[:, col0:]))
+    first = None
+    for o in outs:
+        c = o.copyout(np.uint16, (M, N))
+        assert np.all(c[:, :col0] == 0xFFFF), "columns of another rank were overwritten"
+        assert not np.any(c[:, col0:] == 0xFFFF)
+        assert_close(orc.bf16_to_f32(c[:, col0:]), ref, mk.MK_BF16, "tile-store delivery")
+        first = c if first is None else first
+        assert np.array_equal(c, first), "the copies differ from each other"
+    for x in [A, B] + outs:
+        x.free()

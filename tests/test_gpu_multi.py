@@ -54,24 +54,38 @@ def _worker(rank, world, port, out_dir):
     dev = mk.Device(rank)
     rng = np.random.default_rng(0)                       # identical inputs on every rank
 
-    # ---- GEMM split along N ----
+    # ---- GEMM split along N: a small problem (single-CTA kernel, peers written by the epilogue warps) ----
     M, K, N = 384, 256, 1280
     a, b = orc.normal_bf16(rng, (M, K), 1.0), orc.normal_bf16(rng, (K, N), 0.05)
     A, B = dev.from_numpy(a), dev.from_numpy(b)
     Cfull = dev.from_numpy(np.full((M, N), 0xFFFF, np.uint16))          # poison: every element must be overwritten
+    # ---- ... and one with enough 256 x 256 tiles per rank for the CTA-pair kernel, whose epilogue delivers tiles by
+    # tile stores; rows and columns are ragged against the tile and against the 32 x 64 store boxes ----
+    M2, K2, N2 = 2040, 320, 5128
+    a2, b2 = orc.normal_bf16(rng, (M2, K2), 1.0), orc.normal_bf16(rng, (K2, N2), 0.05)
+    A2, B2 = dev.from_numpy(a2), dev.from_numpy(b2)
+    C2full = dev.from_numpy(np.full((M2, N2), 0xFFFF, np.uint16))
     # ---- attention split by head (GQA 8:4, two kv heads per rank) ----
     Bt, Hq, Hkv, S, D = 1, 8, 4, 320, 128
     q, k, v = orc.normal_bf16(rng, (Bt, Hq, S, D)), orc.normal_bf16(rng, (Bt, Hkv, S, D)), orc.normal_bf16(rng, (Bt, Hkv, S, D))
     Q, Kb, V = dev.from_numpy(q), dev.from_numpy(k), dev.from_numpy(v)
     Ofull = dev.from_numpy(np.full((Bt, Hq, S, D), 0xFFFF, np.uint16))
     dev.sync()
-    ptrs, keep = _open_peers(dev, dist, rank, world, {"c": Cfull, "o": Ofull})
+    ptrs, keep = _open_peers(dev, dist, rank, world, {"c": Cfull, "o": Ofull, "c2": C2full})
     dist.barrier()                                       # poison is in place everywhere before anyone stores
 
     col0, ncols = sharding.gemm_column_shard(N, rank, world)
     peers_c = [p + col0 * 2 for r, p in enumerate(ptrs["c"]) if r != rank]
     dev.gemm(A, B.view(col0 * 2, K * N * 2 - col0 * 2), Cfull, M, ncols, K, mk.MK_BF16, ldb=N, ldc=N,
              c_ptr=Cfull.ptr + col0 * 2, peers=peers_c)
+    c20, n2cols = sharding.gemm_column_shard(N2, rank, world)
+    peers_c2 = [p + c20 * 2 for r, p in enumerate(ptrs["c2"]) if r != rank]
+    dev.profile_begin()
+    dev.gemm(A2, B2.view(c20 * 2, K2 * N2 * 2 - c20 * 2), C2full, M2, n2cols, K2, mk.MK_BF16, ldb=N2, ldc=N2,
+             c_ptr=C2full.ptr + c20 * 2, peers=peers_c2)
+    launched = [name for name, _ in dev.profile_end()]
+    if os.environ.get("MOROK_B200_PEER_TMA", "1") != "0":
+        assert launched == ["gemm_tc_pair_deliver"], launched
     q0, nq, kv0, nkv = sharding.head_shard(Hq, Hkv, rank, world)
     qv = Q.view(q0 * S * D * 2, (Hq - q0) * S * D * 2)
     kv, vv = (t.view(kv0 * S * D * 2, (Hkv - kv0) * S * D * 2) for t in (Kb, V))
@@ -86,6 +100,10 @@ def _worker(rank, world, port, out_dir):
     c = Cfull.copyout(np.uint16, (M, N))
     ref = orc.matmul_f32(bf(a), bf(b))
     assert np.all(np.abs(bf(c) - ref) <= 1e-2 + 2e-2 * np.abs(ref)), "gathered C differs from the oracle"
+    c2 = C2full.copyout(np.uint16, (M2, N2))
+    assert not np.any(c2 == 0xFFFF), "an element of the gathered C (CTA-pair kernel) was never written"
+    ref2 = orc.matmul_f32(bf(a2), bf(b2))
+    assert np.all(np.abs(bf(c2) - ref2) <= 1e-2 + 2e-2 * np.abs(ref2)), "gathered C (tile-store delivery) differs from the oracle"
     o = Ofull.copyout(np.uint16, (Bt, Hq, S, D))
     ref_o = orc.sdpa_f32(bf(q), bf(k), bf(v), causal=True)
     assert np.all(np.abs(bf(o) - ref_o) <= 1e-2 + 2e-2 * np.abs(ref_o)), "gathered O differs from the oracle"

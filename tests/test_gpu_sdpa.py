@@ -235,3 +235,33 @@ def test_decode_reads_a_bshd_cache_in_place(dev):
     o = orc.bf16_to_f32(O.copyout(np.uint16, (B, 1, H, D))).transpose(0, 2, 1, 3)
     ref = orc.sdpa_f32(q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3))
     assert_close(o, ref, mk.MK_BF16, "decode over a [B,S,H,D] cache")
+
+
+@pytest.mark.parametrize("D", [128, 64])
+def test_head_sharded_delivery_by_tile_stores_into_stand_in_peers(dev, D):
+    """The head-sharded form on one GPU: two more buffers of the same GPU stand in for the peers' O.  The kernel
+    computes heads 2 .. 5 of 8 (GQA 2:1) and must deliver them, through its staging tile and one tile store per
+    destination, into all three tensors without touching the other heads; ragged sequence length."""
+    B, H, Hkv, S = 2, 8, 4, 600
+    q0, nq, kv0, nkv = 2, 4, 1, 2
+    rng = np.random.default_rng(D)
+    q, k, v = orc.normal_bf16(rng, (B, H, S, D)), orc.normal_bf16(rng, (B, Hkv, S, D)), orc.normal_bf16(rng, (B, Hkv, S, D))
+    Q, K, V = dev.from_numpy(q), dev.from_numpy(k), dev.from_numpy(v)
+    outs = [dev.from_numpy(np.full((B, H, S, D), 0xFFFF, np.uint16)) for _ in range(3)]
+    off = q0 * S * D * 2
+    dev.sdpa(Q.view(off, (H - q0) * S * D * 2), K.view(kv0 * S * D * 2, (Hkv - kv0) * S * D * 2), V.view(kv0 * S * D * 2, (Hkv - kv0) * S * D * 2),
+             outs[0], B, nq, nkv, S, S, D, dtype=mk.MK_BF16, causal=True,
+             q_strides=(H * S * D, S * D, D), k_strides=(Hkv * S * D, S * D, D), v_strides=(Hkv * S * D, S * D, D),
+             o_strides=(H * S * D, S * D, D), o_ptr=outs[0].ptr + off, peers=[o.ptr + off for o in outs[1:]])
+    assert dev.kernel_status() == 0
+    bf = orc.bf16_to_f32
+    ref = orc.sdpa_f32(bf(q[:, q0:q0 + nq]), bf(k[:, kv0:kv0 + nkv]), bf(v[:, kv0:kv0 + nkv]), causal=True)
+    first = None
+    for o in outs:
+        got = o.copyout(np.uint16, (B, H, S, D))
+        assert np.all(got[:, :q0] == 0xFFFF) and np.all(got[:, q0 + nq:] == 0xFFFF), "heads of another rank were overwritten"
+        assert_close(bf(got[:, q0:q0 + nq]), ref, mk.MK_BF16, "tile-store delivery of O")
+        first = got if first is None else first
+        assert np.array_equal(got, first), "the copies differ from each other"
+    for x in [Q, K, V] + outs:
+        x.free()

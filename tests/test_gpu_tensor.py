@@ -228,36 +228,37 @@ def test_config4_full_size_layer_causal_prefix_vs_oracle(dev):
     assert out.last_launches() == 11
     got = orc.bf16_to_f32(out.as_ndarray()).reshape(batch, seq, hidden)
     assert np.all(np.isfinite(got))
-    # Three oracles.  (1) "kernels": f32 arithmetic, results rounded through bf16 exactly where a kernel of the fused
-    # schedule stores one (norm, each projection, RoPE, attention, residual sums, the gated product) -- the arithmetic
-    # this path implements; the layer is held to the element-wise bar of the bf16 paths (2e-2 relative + 1e-2
-    # absolute) against it.  (2) "ops": rounded after every op, what the dtypes of the reference's bf16 graph dictate
-    # (tensor/src/reduce.rs:673-691).  (3) pure f32 on the bf16-rounded inputs.  Eleven bf16 results in a row, the last
-    # one a sum of 14336 products of rounded activations, put ~1.4e-2 of absolute rounding noise on the output whatever
-    # the implementation: oracles (1) and (2) themselves disagree beyond the element-wise bar on ~4 % of the
-    # elements (small outputs, where the bar is 1e-2), so against (2) and (3) the layer is bounded in relative rms and
-    # must be no further from (3) than (2) is.
+    # The chain as a whole.  Eleven bf16 results in a row, the last one a sum of 14336 products of rounded activations: a
+    # difference in the last bit of one intermediate moves later roundings, and two evaluations that differ anywhere
+    # upstream end ~1e-2 (absolute, rms) apart at the output.  That holds between CPU evaluations as well -- the oracle
+    # rounded after every op (what the dtypes of the reference's bf16 graph dictate, tensor/src/reduce.rs:673-691) and
+    # the oracle rounded only where a fused kernel stores differ beyond 2e-2 rel + 1e-2 abs on ~4 % of the elements -- so
+    # the element-wise bar is applied kernel by kernel on identical inputs (next test) and the chain is bounded in
+    # relative rms: against the pure-f32 oracle it must be no further than the reference's own bf16 arithmetic is.
     for b, prefix in ((0, 160), (7, 96)):
         xs = x[b:b + 1, :prefix]
-        ref_k = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd, round_boundaries="kernels")
         g = got[b:b + 1, :prefix]
-        err = np.abs(g - ref_k)
-        bad = err > 1e-2 + 2e-2 * np.abs(ref_k)
-        assert not bad.any(), (f"config 4, batch element {b}: {int(bad.sum())}/{bad.size} elements beyond 2e-2 rel / 1e-2 abs of the "
-                               f"kernel-boundary oracle; max err {float(err.max()):.4g}, rms {float(np.sqrt(np.mean(err ** 2))):.3e}")
         ref = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd)
         ref_o = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd, round_boundaries="ops")
+        ref_k = orc.decoder_layer_f32(xs, w, 1, prefix, n_q, n_kv, hd, round_boundaries="kernels")
         scale = float(np.sqrt(np.mean(ref ** 2)))
 
         def rms_rel(a, r):
             return float(np.sqrt(np.mean((a - r) ** 2))) / scale
-        d_f32, d_ops, ops_f32 = rms_rel(g, ref), rms_rel(g, ref_o), rms_rel(ref_o, ref)
+
+        def outside(a, r):
+            return float(np.mean(np.abs(a - r) > 1e-2 + 2e-2 * np.abs(r)))
+        d_f32, d_ops, d_k, ops_f32 = rms_rel(g, ref), rms_rel(g, ref_o), rms_rel(g, ref_k), rms_rel(ref_o, ref)
         max_norm = float(np.abs(g - ref).max() / np.abs(ref).max())
-        print(f"config 4 batch element {b}: rms rel vs pure-f32 oracle {d_f32:.3e} (normalised max {max_norm:.3e}), vs per-op "
-              f"bf16 oracle {d_ops:.3e}; per-op bf16 oracle vs pure-f32 oracle {ops_f32:.3e}; vs kernel-boundary oracle {rms_rel(g, ref_k):.3e}")
+        print(f"config 4 batch element {b}: rms rel vs pure-f32 oracle {d_f32:.3e} (normalised max {max_norm:.3e}), vs per-op bf16 "
+              f"oracle {d_ops:.3e}, vs kernel-boundary oracle {d_k:.3e}; per-op bf16 oracle vs pure-f32 oracle {ops_f32:.3e}; fraction "
+              f"outside the element-wise bar: GPU vs per-op oracle {outside(g, ref_o):.3f}, kernel-boundary oracle vs per-op oracle "
+              f"{outside(ref_k, ref_o):.3f}")
         assert d_f32 < 1e-2 and max_norm < 2e-2, f"config 4, batch element {b}: rms rel {d_f32:.3e}, normalised max {max_norm:.3e}"
         assert d_f32 <= ops_f32 * 1.05 + 1e-4, f"further from the f32 oracle ({d_f32:.3e}) than the reference's own bf16 graph is ({ops_f32:.3e})"
-        assert d_ops < 1e-2
+        assert d_ops < 1e-2 and d_k < 1e-2
+        # ... and no further from the reference's bf16 arithmetic than an equally valid CPU evaluation is
+        assert outside(g, ref_o) <= outside(ref_k, ref_o) * 1.25 + 5e-3
     # batch elements are independent: identical inputs give identical outputs
     x2 = x.copy()
     x2[3] = x2[5]
@@ -265,6 +266,67 @@ def test_config4_full_size_layer_causal_prefix_vs_oracle(dev):
     o2 = out2.as_ndarray().reshape(batch, seq, hidden)
     assert np.array_equal(o2[3], o2[5])
     assert np.array_equal(o2[0], out.as_ndarray().reshape(batch, seq, hidden)[0])
+
+
+def test_config4_full_size_every_kernel_elementwise_on_identical_inputs(dev):
+    """Config 4 at full size, kernel by kernel: every intermediate the layer's eleven kernels store is read back, and each
+    kernel's output is compared element-wise (2e-2 relative + 1e-2 absolute) with the oracle's evaluation of THAT op on the
+    inputs the kernel itself consumed (f32 arithmetic, one rounding to bf16 where the kernel stores).  Sampled token
+    prefixes of two batch elements; attention over the prefix's causal window."""
+    batch, seq, n_q, n_kv, hd, hidden, ffn = 8, 2048, 32, 8, 128, 4096, 14336
+    rng = np.random.default_rng(0)
+    x = orc.normal_bf16(rng, (batch, seq, hidden), 1.0)
+    w = orc.decoder_layer_weights(rng, hidden, n_q, n_kv, hd, ffn, sigma=0.02)
+    h0 = Tensor.from_ndarray(dev, x.reshape(batch * seq, hidden))
+    W = {k: Tensor.from_ndarray(dev, v) for k, v in w.items()}
+    cos_np, sin_np = orc.rope_tables(seq, hd)
+    cos = Tensor.from_ndarray(dev, cos_np.reshape(1, seq, 1, hd // 2))
+    sin = Tensor.from_ndarray(dev, sin_np.reshape(1, seq, 1, hd // 2))
+    launches = 0
+
+    def stored(t):          # one kernel per stage: realize it and keep its output
+        nonlocal launches
+        t.realize()
+        launches += t.last_launches()
+        return t
+
+    n1 = stored(h0.rms_norm(-1, 1e-5).cast(mk.MK_BF16))
+    q_pre, k_pre, v_pre = (stored(n1.matmul(W[n])) for n in ("wq", "wk", "wv"))
+    q = stored(q_pre.try_reshape((batch, seq, n_q, hd)).apply_rotary_emb(cos, sin, False))
+    k = stored(k_pre.try_reshape((batch, seq, n_kv, hd)).apply_rotary_emb(cos, sin, False))
+    v = v_pre.try_reshape((batch, seq, n_kv, hd))
+    a = stored(q.try_permute((0, 2, 1, 3)).scaled_dot_product_attention(k.try_permute((0, 2, 1, 3)), v.try_permute((0, 2, 1, 3)), is_causal=True)
+               .try_permute((0, 2, 1, 3)).try_reshape((batch * seq, n_q * hd)))
+    h = stored(h0.try_add(a.matmul(W["wo"])))
+    n2 = stored(h.rms_norm(-1, 1e-5).cast(mk.MK_BF16))
+    ff = stored(n2.matmul(W["wgate"]).silu().try_mul(n2.matmul(W["wup"])))
+    out = stored(h.try_add(ff.matmul(W["wdown"])))
+    assert dev.kernel_status() == 0
+    assert launches == 11
+    bf, rb = orc.bf16_to_f32, orc.round_bf16
+    G = {name: t.as_ndarray() for name, t in dict(n1=n1, q_pre=q_pre, k_pre=k_pre, v=v_pre, q=q, k=k, a=a, h=h, n2=n2, ff=ff, out=out).items()}
+    Wf = {name: bf(v) for name, v in w.items()}
+    xf = bf(x).reshape(batch * seq, hidden)
+    for b, prefix in ((0, 160), (7, 96)):
+        r = slice(b * seq, b * seq + prefix)         # token rows of this prefix
+        tok = lambda name: bf(G[name].reshape(batch * seq, -1)[r])      # noqa: E731
+        checks = {
+            "rms_norm 1": (tok("n1"), rb(orc.rms_norm_f32(xf[r], 1e-5))),
+            "q projection": (tok("q_pre"), rb(orc.matmul_f32(tok("n1"), Wf["wq"]))),
+            "k projection": (tok("k_pre"), rb(orc.matmul_f32(tok("n1"), Wf["wk"]))),
+            "v projection": (tok("v"), rb(orc.matmul_f32(tok("n1"), Wf["wv"]))),
+            "rope q": (tok("q"), rb(orc.rope_f32(tok("q_pre").reshape(1, prefix, n_q, hd), cos_np[:prefix], sin_np[:prefix], False, row_div=n_q)).reshape(prefix, -1)),
+            "rope k": (tok("k"), rb(orc.rope_f32(tok("k_pre").reshape(1, prefix, n_kv, hd), cos_np[:prefix], sin_np[:prefix], False, row_div=n_kv)).reshape(prefix, -1)),
+            "residual 1 (o projection + x)": (tok("h"), rb(xf[r] + orc.matmul_f32(tok("a"), Wf["wo"]))),
+            "rms_norm 2": (tok("n2"), rb(orc.rms_norm_f32(tok("h"), 1e-5))),
+            "gated feed-forward": (tok("ff"), rb(orc.swiglu_f32(orc.matmul_f32(tok("n2"), Wf["wgate"]), orc.matmul_f32(tok("n2"), Wf["wup"])))),
+            "residual 2 (down projection + h)": (tok("out"), rb(tok("h") + orc.matmul_f32(tok("ff"), Wf["wdown"]))),
+        }
+        qh, kh, vh = (np.ascontiguousarray(tok(n).reshape(1, prefix, -1, hd).transpose(0, 2, 1, 3)) for n in ("q", "k", "v"))
+        att = rb(orc.sdpa_f32(qh, kh, vh, causal=True))
+        checks["attention"] = (tok("a"), np.ascontiguousarray(att.transpose(0, 2, 1, 3)).reshape(prefix, -1))
+        for name, (got_k, want) in checks.items():
+            assert_close(got_k, want, mk.MK_BF16, f"config 4, batch element {b}, kernel '{name}'")
 
 
 def test_plan_replay_matches_eager_bit_for_bit(dev):
