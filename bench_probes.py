@@ -27,7 +27,7 @@ def _ints(args, n, default):
     return tuple(vals) if len(vals) == n else default
 
 
-def _timed(dev, fn, warm=3, n=5, stream=None):
+def _timed(dev, fn, warm=3, n=20, stream=None):
     for _ in range(warm):
         fn()
     e0, e1 = mk.Event(dev), mk.Event(dev)

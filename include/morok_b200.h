@@ -53,7 +53,8 @@ enum {
 /* Element types of the dense path (dtype/src/lib.rs:145 ScalarDType::{Float32,BFloat16,Float16}).
  * MK_F8E4M3 / MK_F8E5M2 (dtype/src/lib.rs:142-143, 234-256: finite range +-448 / +-57344) are storage
  * types: inputs of mk_gemm (f32 accumulation, f32 / bf16 / f16 output) and either side of mk_cast. */
-typedef enum { MK_F32 = 0, MK_BF16 = 1, MK_F16 = 2, MK_F8E4M3 = 3, MK_F8E5M2 = 4 } mk_dtype;
+typedef enum { MK_F32 = 0, MK_BF16 = 1, MK_F16 = 2, MK_F8E4M3 = 3, MK_F8E5M2 = 4,
+               MK_BOOL = 5 /* one byte per element; tensors of this type are attention masks only (DType::Bool) */ } mk_dtype;
 
 typedef struct mk_device mk_device;
 typedef struct mk_stream mk_stream;
@@ -366,7 +367,7 @@ typedef struct {
     int64_t k_strides[3];
     int64_t v_strides[3];
     int64_t o_strides[3];
-    const float* mask;    /* optional additive f32 mask [Sq,Sk], broadcast over B and H */
+    const void* mask;     /* optional mask added to the scaled scores; shape and element type: mask_kind below */
     float* lse;           /* optional [B,Hq,Sq] f32: max + log(sum) of the scaled, masked scores */
     /* Sharded delivery (heads split across GPUs): finished O tiles are also stored at the same
      * element offset of each peer_O[i]. */
@@ -377,7 +378,17 @@ typedef struct {
      * current keys uses past_seq_len (onnx/src/registry/transformer.rs:155-162), so a single new
      * query row (Sq = 1, causal_offset = Sk - 1) sees the whole cache. */
     int32_t causal_offset;
+    /* The reference adds any mask that broadcasts against the [B, H, Sq, Sk] scores, and turns a bool mask into
+     * 0 where it is true and -inf where it is false first (tensor/src/transformer.rs:112-124).
+     *   MK_MASK_SQ_SK (0)  additive f32 [Sq, Sk], shared by every batch element and head (mask_strides ignored)
+     *   MK_MASK_F32   (1)  additive f32, element (b, h, i, j) at mask[b * s0 + h * s1 + i * s2 + j]
+     *   MK_MASK_BOOL  (2)  one byte per element at the same index, non-zero = attend, zero = add -inf
+     * with s0, s1, s2 = mask_strides in elements; 0 broadcasts that dimension (a key-padding mask [B, 1, 1, Sk] has
+     * strides {Sk, 0, 0}).  Keys are contiguous.  Masks and softcap run on the tensor-core kernel as well. */
+    int32_t mask_kind;
+    int64_t mask_strides[3];
 } mk_sdpa_desc;
+enum { MK_MASK_SQ_SK = 0, MK_MASK_F32 = 1, MK_MASK_BOOL = 2 };
 
 MK_API mk_status mk_sdpa_fwd(mk_device* dev, mk_stream* s, const mk_sdpa_desc* desc);
 
@@ -490,6 +501,8 @@ MK_API mk_status mk_tensor_from_bytes(mk_device* dev, const void* data, int32_t 
 MK_API mk_status mk_tensor_free(mk_tensor* t);
 MK_API mk_status mk_tensor_shape(mk_tensor* t, int64_t* shape /* MK_MAX_DIMS */, int32_t* ndim, int32_t* dtype);
 MK_API mk_status mk_tensor_matmul(mk_tensor* a, mk_tensor* b, mk_tensor** out);
+/* mask: NULL, or a tensor of 2 to 4 dimensions that broadcasts against [B, H, Sq, Sk] (each dimension equal to the
+ * score's or 1; missing leading dimensions count as 1), floating point (added) or MK_BOOL (true attends). */
 MK_API mk_status mk_tensor_sdpa(mk_tensor* q, mk_tensor* k, mk_tensor* v, mk_tensor* mask /* or NULL */,
                                 float scale /* <= 0: default */, int32_t causal, float softcap, mk_tensor** out);
 MK_API mk_status mk_tensor_rms_norm(mk_tensor* x, float eps, mk_tensor** out);

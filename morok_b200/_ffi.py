@@ -15,7 +15,8 @@ LIB_PATH = os.environ.get("MOROK_B200_LIB") or os.path.join(HERE, "libmorok_b200
 
 MK_OK, MK_ERR_INVALID, MK_ERR_CUDA, MK_ERR_OOM = 0, -1, -2, -3
 MK_ERR_SIZE_MISMATCH, MK_ERR_NOT_ALLOCATED, MK_ERR_TIMEOUT, MK_ERR_UNSUPPORTED, MK_ERR_KERNEL = -4, -5, -6, -7, -8
-MK_F32, MK_BF16, MK_F16, MK_F8E4M3, MK_F8E5M2 = 0, 1, 2, 3, 4
+MK_F32, MK_BF16, MK_F16, MK_F8E4M3, MK_F8E5M2, MK_BOOL = 0, 1, 2, 3, 4, 5
+MK_MASK_SQ_SK, MK_MASK_F32, MK_MASK_BOOL = 0, 1, 2
 MK_ALLOC_ZERO_INIT = 1
 MK_EPI_NONE, MK_EPI_ADD, MK_EPI_ADD_ROW, MK_EPI_SWIGLU = 0, 1, 2, 3
 MK_GEMM_SCALED, MK_GEMM_GATE_SIGMOID = 1, 2
@@ -50,7 +51,8 @@ class SdpaDesc(C.Structure):
                 ("Dv", i32), ("scale", f32), ("causal", i32), ("softcap", f32),
                 ("Q", vp), ("K", vp), ("V", vp), ("O", vp),
                 ("q_strides", i64 * 3), ("k_strides", i64 * 3), ("v_strides", i64 * 3), ("o_strides", i64 * 3),
-                ("mask", vp), ("lse", vp), ("n_peers", i32), ("peer_O", vp * MK_MAX_PEERS), ("causal_offset", i32)]
+                ("mask", vp), ("lse", vp), ("n_peers", i32), ("peer_O", vp * MK_MAX_PEERS), ("causal_offset", i32),
+                ("mask_kind", i32), ("mask_strides", i64 * 3)]
 
 
 class GemmTuning(C.Structure):

@@ -70,6 +70,8 @@ mk_status mk_sdpa_fwd(mk_device* dev, mk_stream* s, const mk_sdpa_desc* desc) {
     if (d.B == 0 || d.Hq == 0 || d.Sq == 0) return MK_OK;
     MK_REQUIRE(d.Q && d.O && (d.Sk == 0 || (d.K && d.V)), "mk_sdpa_fwd: null tensor");
     for (int i = 0; i < d.n_peers; ++i) MK_REQUIRE(d.peer_O[i], "mk_sdpa_fwd: peer_O[%d] is null", i);
+    MK_REQUIRE(d.mask_kind >= MK_MASK_SQ_SK && d.mask_kind <= MK_MASK_BOOL, "mk_sdpa_fwd: unknown mask_kind %d", d.mask_kind);
+    MK_REQUIRE(!d.mask || (d.mask_strides[0] >= 0 && d.mask_strides[1] >= 0 && d.mask_strides[2] >= 0), "mk_sdpa_fwd: negative mask stride");
     const float scale = d.scale > 0.0f ? d.scale : 1.0f / std::sqrt((float)d.D);
     if (dev->mock) return fail(MK_ERR_CUDA, "mk_sdpa_fwd: no CUDA device (mock devices run no kernels)");
     MK_CUDA(cudaSetDevice(dev->ordinal));

@@ -36,7 +36,7 @@ mk_status cuda_fail(cudaError_t e, const char* what);
     } while (0)
 
 inline bool dtype_is_fp8(int32_t dt) { return dt == MK_F8E4M3 || dt == MK_F8E5M2; }
-inline size_t dtype_size(int32_t dt) { return dt == MK_F32 ? 4 : dtype_is_fp8(dt) ? 1 : 2; }
+inline size_t dtype_size(int32_t dt) { return dt == MK_F32 ? 4 : (dtype_is_fp8(dt) || dt == MK_BOOL) ? 1 : 2; }
 // The types every operation computes in; the 8-bit floats are storage types that only mk_gemm (as
 // inputs) and mk_cast accept.
 inline bool dtype_valid(int32_t dt) { return dt == MK_F32 || dt == MK_BF16 || dt == MK_F16; }

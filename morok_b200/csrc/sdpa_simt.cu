@@ -56,6 +56,11 @@ __global__ void __launch_bounds__(WARPS * 32) sdpa_simt_kernel(const SimtSdpa P)
         const T* kb = (const T*)d.K + b * d.k_strides[0] + hk * d.k_strides[1];
         const T* vb = (const T*)d.V + b * d.v_strides[0] + hk * d.v_strides[1];
         const int64_t o_off = b * d.o_strides[0] + h * d.o_strides[1] + i * d.o_strides[2];
+        // this row's mask values (tensor/src/transformer.rs:112-124): additive f32, or bool where false adds -inf
+        const int64_t m_off = d.mask_kind == MK_MASK_SQ_SK ? (int64_t)i * d.Sk
+                                                           : b * d.mask_strides[0] + h * d.mask_strides[1] + i * d.mask_strides[2];
+        const float* mask_f = (d.mask && d.mask_kind != MK_MASK_BOOL) ? (const float*)d.mask + m_off : nullptr;
+        const unsigned char* mask_b = (d.mask && d.mask_kind == MK_MASK_BOOL) ? (const unsigned char*)d.mask + m_off : nullptr;
 
         __syncwarp();
         for (int x = lane; x < d.D; x += 32) sq[warp][x] = ldf<T>(q, x);
@@ -81,7 +86,8 @@ __global__ void __launch_bounds__(WARPS * 32) sdpa_simt_kernel(const SimtSdpa P)
                 for (int x = 0; x < d.D; ++x) acc = fmaf(sq[warp][x], ldf<T>(kr, x), acc);
                 s = acc * P.scale;
                 if (d.causal && j > last_col) s = -CUDART_INF_F;
-                if (d.mask) s += d.mask[(int64_t)i * d.Sk + j];
+                if (mask_f) s += mask_f[j];
+                if (mask_b && !mask_b[j]) s = -CUDART_INF_F;
                 if (d.softcap > 0.0f) s = tanhf(s / d.softcap) * d.softcap;
             }
             float mx = s;

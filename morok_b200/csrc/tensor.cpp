@@ -290,7 +290,18 @@ mk_status run_sdpa(Node& n, bool store_bshd) {
     NodeP md;
     if (mask) {
         if ((st = dense(mask, &md)) != MK_OK || (st = node_ptr(*md, &pm)) != MK_OK) return st;
-        d.mask = (const float*)pm;
+        d.mask = pm;
+        // the mask broadcasts against [B, H, Sq, Sk] (tensor/src/transformer.rs:112-124): right-align its shape, a
+        // dimension of 1 repeats (stride 0), the others step through the dense data
+        d.mask_kind = md->dtype == MK_BOOL ? MK_MASK_BOOL : MK_MASK_F32;
+        const int lead = 4 - md->ndim();
+        int64_t acc = md->shape.back();       // == Sk (checked when the graph was built)
+        for (int dim = 2; dim >= 0; --dim) {  // query row, head, batch
+            const int j = dim - lead;         // index into the mask's own shape
+            const int64_t extent = j >= 0 ? md->shape[j] : 1;
+            d.mask_strides[dim] = extent == 1 ? 0 : acc;
+            acc *= extent;
+        }
     }
     if ((st = alloc_output(n)) != MK_OK || (st = node_ptr(n, &po)) != MK_OK) return st;
     const int64_t H = d.Hq, S = d.Sq, Dv = d.Dv;
@@ -552,7 +563,7 @@ extern "C" {
 
 mk_status mk_tensor_from_bytes(mk_device* dev, const void* data, int32_t dtype, const int64_t* shape, int32_t ndim, mk_tensor** out) {
     MK_REQUIRE(dev && out && (shape || ndim == 0), "mk_tensor_from_bytes: null argument");
-    MK_REQUIRE(dtype_valid(dtype), "mk_tensor_from_bytes: unknown dtype %d", dtype);
+    MK_REQUIRE(dtype_valid(dtype) || dtype == MK_BOOL, "mk_tensor_from_bytes: unknown dtype %d", dtype);
     MK_REQUIRE(ndim >= 0 && ndim <= MK_MAX_DIMS, "mk_tensor_from_bytes: ndim %d out of range", ndim);
     auto n = std::make_shared<Node>();
     n->op = LEAF;
@@ -640,8 +651,15 @@ mk_status mk_tensor_sdpa(mk_tensor* qt, mk_tensor* kt, mk_tensor* vt, mk_tensor*
     n->in = {q, k, v};
     if (maskt) {
         NodeP m = maskt->node;
-        MK_REQUIRE(m->ndim() == 2 && m->shape[0] == q->shape[2] && m->shape[1] == k->shape[2], "scaled_dot_product_attention: mask must be [Sq,Sk]");
-        n->in.push_back(make_cast(m, MK_F32));
+        MK_REQUIRE(m->ndim() >= 2 && m->ndim() <= 4, "scaled_dot_product_attention: the mask needs 2 to 4 dimensions, got %d", m->ndim());
+        MK_REQUIRE(m->shape.back() == k->shape[2], "scaled_dot_product_attention: the mask's last dimension must be Sk = %lld", (long long)k->shape[2]);
+        const int64_t want[3] = {q->shape[0], q->shape[1], q->shape[2]};      // B, H, Sq
+        for (int j = 0; j < m->ndim() - 1; ++j) {
+            const int64_t w = want[3 - (m->ndim() - 1) + j];
+            MK_REQUIRE(m->shape[j] == 1 || m->shape[j] == w, "scaled_dot_product_attention: mask dimension %d is %lld, expected 1 or %lld", j,
+                       (long long)m->shape[j], (long long)w);
+        }
+        n->in.push_back(m->dtype == MK_BOOL ? m : make_cast(m, MK_F32));     // bool: true attends; anything else is added as f32
     }
     *out = wrap(n);
     return MK_OK;

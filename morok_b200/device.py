@@ -14,10 +14,10 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import MK_BF16, MK_F16, MK_F32, MK_F8E4M3, MK_F8E5M2, check
+from ._ffi import MK_BF16, MK_BOOL, MK_F16, MK_F32, MK_F8E4M3, MK_F8E5M2, check
 
-_NP_OF = {MK_F32: np.float32, MK_BF16: np.uint16, MK_F16: np.float16, MK_F8E4M3: np.uint8, MK_F8E5M2: np.uint8}
-_SIZE_OF = {MK_F32: 4, MK_BF16: 2, MK_F16: 2, MK_F8E4M3: 1, MK_F8E5M2: 1}
+_NP_OF = {MK_F32: np.float32, MK_BF16: np.uint16, MK_F16: np.float16, MK_F8E4M3: np.uint8, MK_F8E5M2: np.uint8, MK_BOOL: np.bool_}
+_SIZE_OF = {MK_F32: 4, MK_BF16: 2, MK_F16: 2, MK_F8E4M3: 1, MK_F8E5M2: 1, MK_BOOL: 1}
 
 
 def dtype_size(dt: int) -> int:
@@ -266,7 +266,10 @@ class Device:
              Dv: Optional[int] = None, dtype: int = MK_BF16, scale: float = 0.0, causal: bool = False,
              softcap: float = 0.0, mask: Optional[Buffer] = None, lse: Optional[Buffer] = None,
              q_strides=None, k_strides=None, v_strides=None, o_strides=None, peers: Sequence[int] = (),
-             stream: Optional[Stream] = None, o_ptr: Optional[int] = None, causal_offset: int = 0):
+             stream: Optional[Stream] = None, o_ptr: Optional[int] = None, causal_offset: int = 0,
+             mask_strides: Optional[Sequence[int]] = None, mask_bool: bool = False):
+        """mk_sdpa_fwd.  mask: additive f32 [Sq, Sk] by default; with mask_strides = (batch, head, row) element strides
+        (0 broadcasts) any shape that broadcasts against [B, Hq, Sq, Sk]; mask_bool: one byte per element, non-zero attends."""
         Dv = D if Dv is None else Dv
         d = _ffi.SdpaDesc()
         d.dtype, d.B, d.Hq, d.Hkv, d.Sq, d.Sk, d.D, d.Dv = dtype, B, Hq, Hkv, Sq, Sk, D, Dv
@@ -281,6 +284,10 @@ class Device:
             for i, x in enumerate(val if val is not None else dflt):
                 arr[i] = x
         d.mask = mask.ptr if mask is not None else None
+        if mask is not None and (mask_strides is not None or mask_bool):
+            d.mask_kind = _ffi.MK_MASK_BOOL if mask_bool else _ffi.MK_MASK_F32
+            for i, x in enumerate(mask_strides if mask_strides is not None else (0, 0, Sk)):
+                d.mask_strides[i] = x
         d.lse = lse.ptr if lse is not None else None
         d.n_peers = len(peers)
         for i, p in enumerate(peers):

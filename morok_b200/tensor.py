@@ -15,10 +15,10 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _ffi
-from ._ffi import MK_BF16, MK_F16, MK_F32, check
+from ._ffi import MK_BF16, MK_BOOL, MK_F16, MK_F32, check
 from .device import Device
 
-_NP = {MK_F32: np.float32, MK_BF16: np.uint16, MK_F16: np.float16}
+_NP = {MK_F32: np.float32, MK_BF16: np.uint16, MK_F16: np.float16, MK_BOOL: np.bool_}
 
 
 def _i64(vals: Sequence[int]):
@@ -50,7 +50,8 @@ class Tensor:
         """f32 / f16 arrays map to their dtype; uint16 arrays are bf16 bit patterns."""
         arr = np.ascontiguousarray(arr)
         if dtype is None:
-            dtype = {np.dtype(np.float32): MK_F32, np.dtype(np.float16): MK_F16, np.dtype(np.uint16): MK_BF16}.get(arr.dtype)
+            dtype = {np.dtype(np.float32): MK_F32, np.dtype(np.float16): MK_F16, np.dtype(np.uint16): MK_BF16,
+                     np.dtype(np.bool_): MK_BOOL}.get(arr.dtype)      # bool arrays are attention masks (DType::Bool)
             if dtype is None:
                 raise TypeError(f"unsupported array dtype {arr.dtype}")
         h = C.c_void_p()
@@ -123,7 +124,8 @@ class Tensor:
                                      scale: Optional[float] = None, is_causal: bool = False,
                                      softcap: Optional[float] = None) -> "Tensor":
         """tensor/src/transformer.rs:78-137.  Q [B,H,Sq,D], K [B,Hkv,Sk,D], V [B,Hkv,Sk,Dv]; Hkv may
-        divide H (the caller-side GQA expansion of the reference is folded into the kernel)."""
+        divide H (the caller-side GQA expansion of the reference is folded into the kernel).  attn_mask: 2 to 4
+        dimensions broadcastable against [B,H,Sq,Sk]; a bool tensor attends where true, any other is added."""
         return self._unary(self._dev.lib.mk_tensor_sdpa, key._h, value._h, attn_mask._h if attn_mask is not None else None,
                            float(scale) if scale else 0.0, int(is_causal), float(softcap) if softcap else 0.0)
 

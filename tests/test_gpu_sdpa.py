@@ -265,3 +265,95 @@ def test_head_sharded_delivery_by_tile_stores_into_stand_in_peers(dev, D):
         assert np.array_equal(got, first), "the copies differ from each other"
     for x in [Q, K, V] + outs:
         x.free()
+
+
+def oracle_sdpa_broadcast_mask(q, k, v, mask4, causal, softcap=0.0, scale=None):
+    """The oracle takes one [Sq, Sk] mask; a mask that broadcasts over batch and head is applied pair by pair
+    (bool masks become 0 / -inf first, tensor/src/transformer.rs:112-124)."""
+    B, H, Sq, _ = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    g = H // Hkv
+    if mask4.dtype == np.bool_:
+        mask4 = np.where(mask4, np.float32(0), np.float32(-np.inf))
+    m = np.broadcast_to(mask4, (B, H, Sq, Sk))
+    out = np.empty((B, H, Sq, v.shape[3]), np.float32)
+    for b in range(B):
+        for h in range(H):
+            out[b, h] = orc.sdpa_f32(q[b:b + 1, h:h + 1], k[b:b + 1, h // g:h // g + 1], v[b:b + 1, h // g:h // g + 1], causal=causal,
+                                     mask=np.ascontiguousarray(m[b, h]), softcap=softcap, scale=scale)[0, 0]
+    return out
+
+
+def mask_strides(shape4, Sk):
+    """Element strides (batch, head, row) of a dense mask of shape [b, h, s, Sk] where b, h, s may be 1 (broadcast)."""
+    b, h, s, _ = shape4
+    return (0 if b == 1 else h * s * Sk, 0 if h == 1 else s * Sk, 0 if s == 1 else Sk)
+
+
+@pytest.mark.parametrize("case", [
+    # name, B, Hq, Hkv, Sq, Sk, D, mask shape (b, h, s), bool?, causal, softcap
+    ("key padding per batch element, f32", 3, 4, 2, 384, 384, 128, (3, 1, 1), False, False, 0.0),
+    ("key padding per batch element, bool, causal", 2, 4, 4, 300, 300, 128, (2, 1, 1), True, True, 0.0),
+    ("one [Sq, Sk] mask for all heads", 1, 2, 1, 256, 320, 128, (1, 1, 256), False, False, 0.0),
+    ("full [B, H, Sq, Sk] mask, ragged Sk (unaligned rows)", 2, 2, 2, 130, 203, 64, (2, 2, 130), False, True, 0.0),
+    ("softcap only", 1, 4, 2, 256, 512, 128, None, False, False, 30.0),
+    ("softcap under a causal rule: masked scores become -cap and take part", 1, 2, 2, 384, 384, 128, None, False, True, 20.0),
+    ("bool mask and softcap, head size 64", 2, 2, 1, 200, 264, 64, (2, 1, 200), True, False, 15.0),
+])
+def test_masks_and_softcap_run_on_the_tensor_core_kernel(dev, case):
+    name, B, H, Hkv, Sq, Sk, D, mshape, is_bool, causal, cap = case
+    rng = np.random.default_rng(len(name) + Sq)
+    q, k, v = (orc.round_bf16(rng.standard_normal(s, dtype=np.float32)) for s in ((B, H, Sq, D), (B, Hkv, Sk, D), (B, Hkv, Sk, D)))
+    mask4 = None
+    if mshape is not None:
+        shape4 = (mshape[0], mshape[1], mshape[2], Sk)
+        if is_bool:
+            mask4 = rng.random(shape4) > 0.3
+            mask4[..., 0] = True                                 # key 0 stays visible: no row is masked out entirely
+            if mshape[2] == 1:                                   # a padding mask: hide the tail of each sequence
+                mask4[:] = True
+                for b in range(shape4[0]):
+                    mask4[b, ..., Sk - 17 * (b + 1):] = False
+        else:
+            mask4 = (rng.standard_normal(shape4) * 2).astype(np.float32)
+            if mshape[2] == 1:
+                mask4[:] = 0
+                for b in range(shape4[0]):
+                    mask4[b, ..., Sk - 23 * (b + 1):] = -np.inf
+    Q, K, V = (dev.from_numpy(orc.f32_to_bf16(t)) for t in (q, k, v))
+    O = dev.alloc(B * H * Sq * D * 2)
+    kw = {}
+    if mask4 is not None:
+        kw = dict(mask=dev.from_numpy(mask4), mask_strides=mask_strides(mask4.shape, Sk), mask_bool=is_bool)
+    dev.profile_begin()
+    dev.sdpa(Q, K, V, O, B, H, Hkv, Sq, Sk, D, dtype=mk.MK_BF16, causal=causal, softcap=cap, **kw)
+    launched = [n for n, _ in dev.profile_end()]
+    assert launched == [f"sdpa_tc_d{D}_general"], launched
+    assert dev.kernel_status() == 0
+    got = orc.bf16_to_f32(O.copyout(np.uint16, (B, H, Sq, D)))
+    if mask4 is None:
+        ref = orc.sdpa_f32(q, k, v, causal=causal, softcap=cap)
+    else:
+        ref = oracle_sdpa_broadcast_mask(q, k, v, mask4, causal, cap)
+    assert_close(got, ref, mk.MK_BF16, name)
+
+
+def test_tensor_api_takes_broadcast_and_bool_masks(dev):
+    """`scaled_dot_product_attention(attn_mask=...)` with a bool key-padding mask [B, 1, 1, Sk] and with an additive
+    [Sq, Sk] mask (tensor/src/transformer.rs:112-124), one kernel each."""
+    from morok_b200 import Tensor
+    B, H, S, D = 2, 4, 256, 128
+    rng = np.random.default_rng(8)
+    q, k, v = (orc.round_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32)) for _ in range(3))
+    T = lambda x: Tensor.from_ndarray(dev, orc.f32_to_bf16(x))      # noqa: E731
+    pad = np.ones((B, 1, 1, S), np.bool_)
+    pad[0, ..., 200:] = False
+    pad[1, ..., 131:] = False
+    out = T(q).scaled_dot_product_attention(T(k), T(v), attn_mask=Tensor.from_ndarray(dev, pad), is_causal=True).realize()
+    assert out.last_launches() == 1
+    assert_close(orc.bf16_to_f32(out.as_ndarray()), oracle_sdpa_broadcast_mask(q, k, v, pad, True), mk.MK_BF16, "bool padding mask")
+    add = (rng.standard_normal((S, S)) * 3).astype(np.float32)
+    out = T(q).scaled_dot_product_attention(T(k), T(v), attn_mask=Tensor.from_ndarray(dev, add)).realize()
+    assert_close(orc.bf16_to_f32(out.as_ndarray()), orc.sdpa_f32(q, k, v, mask=add), mk.MK_BF16, "additive [Sq, Sk] mask")
+    with pytest.raises(mk.MorokError):       # a mask that does not broadcast is refused when the graph is built
+        T(q).scaled_dot_product_attention(T(k), T(v), attn_mask=Tensor.from_ndarray(dev, np.zeros((3, S, S), np.float32)))
