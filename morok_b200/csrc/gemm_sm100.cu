@@ -447,6 +447,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t tmem_base = *tmem_slot;
 
     constexpr int BKE = F8 ? 2 * BK : BK;            // elements of K per 128-byte row of a stage
+    constexpr int NB = F8 ? 128 : 64;                // elements of N per 128-byte row ([K, N] weights: an MN-major operand)
+    constexpr int KSTEP = F8 ? 32 : 16;              // elements of K per MMA
     const int num_kb = (int)((p.K + BKE - 1) / BKE);
     const int splits = p.splits > 1 ? p.splits : 1;
     const int kbps = p.splits > 1 ? p.kb_per_split : num_kb;     // k-blocks per unit
@@ -474,8 +476,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                         if constexpr (TRANS_B) {
                             tma_load_2d(sb, &tmB, full, kb * BKE, n0);
                         } else {
+                            // [K, N] weights: boxes of one 128-byte row along N (64 two-byte or 128 one-byte elements) x all k of the stage
 #pragma unroll
-                            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmB, full, n0 + j * 64, kb * BK);
+                            for (int j = 0; j < BN / NB; ++j) tma_load_2d(sb + j * (BKE * 128), &tmB, full, n0 + j * NB, kb * BKE);
                         }
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -489,7 +492,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t leader = elect_one_u32();
             const uint32_t tm = __reduce_max_sync(0xffffffffu, tmem_base);
             const uint64_t adesc0 = smem_desc_sw128(smem_base, 16, 1024);
-            const uint64_t bdesc0 = TRANS_B ? smem_desc_sw128(smem_base + A_BYTES, 16, 1024) : smem_desc_sw128(smem_base + A_BYTES, BK * 128, 1024);
+            const uint64_t bdesc0 = TRANS_B ? smem_desc_sw128(smem_base + A_BYTES, 16, 1024) : smem_desc_sw128(smem_base + A_BYTES, BKE * 128, 1024);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -507,7 +510,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {   // four 32-byte steps along K per stage, for 16- and 8-bit inputs alike
                         const uint64_t adesc = adesc0 + (soff + ((ks * 32) >> 4));
-                        const uint64_t bdesc = bdesc0 + (soff + ((TRANS_B ? ks * 32 : ks * (16 * 128)) >> 4));
+                        const uint64_t bdesc = bdesc0 + (soff + ((TRANS_B ? ks * 32 : ks * (KSTEP * 128)) >> 4));
                         if constexpr (F8) mma_f8_ss_lead(d_tmem, adesc, bdesc, p.idesc, ((kb - kb0) | ks) != 0 ? 1u : 0u, leader);
                         else mma_f16_ss_lead(d_tmem, adesc, bdesc, p.idesc, ((kb - kb0) | ks) != 0 ? 1u : 0u, leader);
                     }
@@ -676,6 +679,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
 
     constexpr int BKE = F8 ? 2 * BK : BK;            // elements of K per 128-byte row of a stage
+    constexpr int NB = F8 ? 128 : 64;                // elements of N per 128-byte row ([K, N] weights: an MN-major operand)
+    constexpr int KSTEP = F8 ? 32 : 16;              // elements of K per MMA
     const int num_kb = (int)((p.K + BKE - 1) / BKE);
     const int num_tiles = p.tiles_m2 * p.tiles_n;   // 256 x 256 tiles, one per cluster and step
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
@@ -704,7 +709,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                             tma_load_2d_pair(sb, tmBr, full, kb * BKE, n0);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < BN / 2 / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), tmBr, full, n0 + j * 64, kb * BK);
+                            for (int j = 0; j < BN / 2 / NB; ++j) tma_load_2d_pair(sb + j * (BKE * 128), tmBr, full, n0 + j * NB, kb * BKE);
                         }
                     }
                     if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
@@ -717,7 +722,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t tm = __reduce_max_sync(0xffffffffu, tmem_base);
             const uint32_t peer_empty = map_to_cta(bar_empty, peer), peer_tfull = map_to_cta(bar_tfull, peer);
             const uint64_t adesc0 = smem_desc_sw128(smem_base, 16, 1024);
-            const uint64_t bdesc0 = TRANS_B ? smem_desc_sw128(smem_base + P_A_BYTES, 16, 1024) : smem_desc_sw128(smem_base + P_A_BYTES, BK * 128, 1024);
+            const uint64_t bdesc0 = TRANS_B ? smem_desc_sw128(smem_base + P_A_BYTES, 16, 1024) : smem_desc_sw128(smem_base + P_A_BYTES, BKE * 128, 1024);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -734,7 +739,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks) {   // four 32-byte steps along K per stage, for 16- and 8-bit inputs alike
                         const uint64_t adesc = adesc0 + (soff + ((ks * 32) >> 4));
-                        const uint64_t bdesc = bdesc0 + (soff + ((TRANS_B ? ks * 32 : ks * (16 * 128)) >> 4));
+                        const uint64_t bdesc = bdesc0 + (soff + ((TRANS_B ? ks * 32 : ks * (KSTEP * 128)) >> 4));
                         if constexpr (F8) mma_f8_ss_pair_lead(d_tmem, adesc, bdesc, p.idesc2, (kb | ks) != 0 ? 1u : 0u, leader);
                         else mma_f16_ss_pair_lead(d_tmem, adesc, bdesc, p.idesc2, (kb | ks) != 0 ? 1u : 0u, leader);
                     }
@@ -960,8 +965,7 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
     if (dev->prop.major != 10) return MK_OK;
     const bool f8 = dtype_is_fp8(d.dtype_in);
     if (d.dtype_in != MK_BF16 && d.dtype_in != MK_F16 && !f8) return MK_OK;
-    // 8-bit inputs run on the tensor cores in the `linear` form only (weights [N, K], both operands K-major)
-    if (f8 && !d.trans_b) return MK_OK;
+    // 8-bit [K, N] weights are an MN-major operand like their 16-bit form: rows of 128 elements along N
     if (d.M <= 0 || d.N <= 0 || d.K <= 0) return MK_OK;
     // TMA needs 16-byte aligned bases and row pitches.
     const int64_t es_in = f8 ? 1 : 2, row_align = 16 / es_in;
@@ -993,13 +997,13 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
         const bool pair = dual || ((tune.pair >= 0 && d.M > BM) ? tune.pair != 0 : use_pair(d, dev->prop.multiProcessorCount));
         // [N,K] weights: one box holds all the rows a CTA needs -- 256 for a single CTA, 128 in a pair
         if (d.trans_b) s1 = encode_2d(&tb, d.dtype_in, B, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.ldb * es_in, bke, pair ? BN / 2 : BN);
-        else s1 = encode_2d(&tb, d.dtype_in, B, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb * 2, 64, BK);
+        else s1 = encode_2d(&tb, d.dtype_in, B, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb * es_in, f8 ? 128 : 64, bke);
         if (s1 != MK_OK) return s1;
         alignas(64) CUtensorMap tb2 = tb;
         if (dual) {
             const char* B2 = (const char*)d.B2 + (size_t)b * d.stride_b * es_in;
             if (d.trans_b) s1 = encode_2d(&tb2, d.dtype_in, B2, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)d.ldb * es_in, bke, BN / 2);
-            else s1 = encode_2d(&tb2, d.dtype_in, B2, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb * 2, 64, BK);
+            else s1 = encode_2d(&tb2, d.dtype_in, B2, (uint64_t)d.N, (uint64_t)d.K, (uint64_t)d.ldb * es_in, f8 ? 128 : 64, bke);
             if (s1 != MK_OK) return s1;
         }
 
@@ -1060,7 +1064,8 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
             ps.kb_per_split = kb_per_split;
             ps.staged = staged_ok(ps, 4);
             mk_status s3;
-            if (f8) s3 = launch_tc<true, MK_F32, true>(dev, st, ta, tb, ps);
+            if (f8 && !d.trans_b) s3 = launch_tc<false, MK_F32, true>(dev, st, ta, tb, ps);
+            else if (f8) s3 = launch_tc<true, MK_F32, true>(dev, st, ta, tb, ps);
             else if (d.trans_b) s3 = launch_tc<true, MK_F32>(dev, st, ta, tb, ps);
             else s3 = launch_tc<false, MK_F32>(dev, st, ta, tb, ps);
             if (s3 == MK_OK) {
@@ -1095,13 +1100,17 @@ mk_status gemm_sm100(mk_device* dev, cudaStream_t st, const mk_gemm_desc& d, boo
         mk_status s2;
 #define MK_TC(TB, OUT) s2 = pair ? launch_tc_pair<TB, OUT>(dev, st, ta, tb, tb2, p) : launch_tc<TB, OUT>(dev, st, ta, tb, p)
 #define MK_TC8(OUT) s2 = pair ? launch_tc_pair<true, OUT, true>(dev, st, ta, tb, tb2, p) : launch_tc<true, OUT, true>(dev, st, ta, tb, p)
-        if (f8) {
+#define MK_TC8N(OUT) s2 = pair ? launch_tc_pair<false, OUT, true>(dev, st, ta, tb, tb2, p) : launch_tc<false, OUT, true>(dev, st, ta, tb, p)
+        if (f8 && !d.trans_b) {
+            if (d.dtype_out == MK_F32) MK_TC8N(MK_F32); else if (d.dtype_out == MK_BF16) MK_TC8N(MK_BF16); else MK_TC8N(MK_F16);
+        } else if (f8) {
             if (d.dtype_out == MK_F32) MK_TC8(MK_F32); else if (d.dtype_out == MK_BF16) MK_TC8(MK_BF16); else MK_TC8(MK_F16);
         } else if (d.trans_b) {
             if (d.dtype_out == MK_F32) MK_TC(true, MK_F32); else if (d.dtype_out == MK_BF16) MK_TC(true, MK_BF16); else MK_TC(true, MK_F16);
         } else {
             if (d.dtype_out == MK_F32) MK_TC(false, MK_F32); else if (d.dtype_out == MK_BF16) MK_TC(false, MK_BF16); else MK_TC(false, MK_F16);
         }
+#undef MK_TC8N
 #undef MK_TC8
 #undef MK_TC
         if (s2 != MK_OK) return s2;

@@ -11,8 +11,8 @@
 //                    its 128 scores in tensor memory, then the scores again 32 columns at a time:
 //                    exp2 (three pairs in four on the special-function unit, the fourth as a
 //                    polynomial on the FMA pipes), P (16 bit) written back over S, m and l in
-//                    registers; O is rescaled only when the maximum moved by > 2^8.  After the last key
-//                    block of an item they publish 1 / l and go straight on to the next item
+//                    registers; O is rescaled only when the maximum moved by > 2^8; finally O is
+//                    normalised and stored (128-bit stores, also to peer GPUs)
 //   warp 8           TMA producer: claims work items, Q per item, then K / V blocks of 128 keys
 //                    through a ring that runs on across items
 //   warp 9           MMA issuer: S_t = Q_t K^T and O_t += P_t V, tile 0 and tile 1 interleaved so the
@@ -20,16 +20,9 @@
 //                    the loops and waits (descriptors then live in uniform registers); one elected
 //                    lane is predicated on the tcgen05 instructions
 //   warp 10          tensor-memory allocation (512 columns: S0 S1 at 0 / 128, O0 O1 at 256 / 384)
-//   warps 12-15      epilogue: O_t / l -> 16 bit -> a staging tile in shared memory -> one tile store per
-//                    destination (the local O and, for head-sharded runs, every peer GPU's O over NVLink),
-//                    off the softmax warps' critical path
-// Registers are rebalanced at start-up (setmaxnreg): the softmax warpgroups take 184 each, the others give up
-// what they do not need.
 //
 // K is a K-major B operand, V an MN-major one (read as stored, no transpose), P is the A operand
 // taken from tensor memory.  Key blocks entirely above the causal diagonal are never loaded.
-// An additive or bool mask and a softcap run in the same kernel (general form: the scores are first
-// rewritten in tensor memory with the mask and the cap applied).
 // All barrier waits are bounded; a wait that gives up records a code in the device error word.
 #include <cstdlib>
 
@@ -53,16 +46,16 @@ struct Cfg {
     static constexpr int SMEM_K = KV_STAGES * TILE_BYTES;
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
     static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 2;
-    // operands, the output staging tile (one 128-row tile, 32 rows per epilogue warp), 1 / l of both tiles,
-    // barriers and slots, alignment slack
-    static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + TILE_BYTES + 1024 + 512 + 1024;
+    static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + 1024 + 512;      // + alignment slack + barriers and slots
+    // head-sharded runs that deliver O by tile stores stage one 128-row tile of output beside the operands
+    static constexpr int SMEM_BYTES_DELIVER = SMEM_BYTES + TILE_BYTES;
 };
 // Tensor maps of the output as every destination sees it: [0] the local O, [1 ..] the peers' O
-// ([B, H, S, D] with the caller's strides; box of 64 columns x 32 rows, 128-byte swizzle).
+// ([B, H, S, D] with the caller's strides; box of 64 columns x 128 rows, 128-byte swizzle).
 struct OStoreMaps {
     CUtensorMap m[1 + MK_MAX_PEERS];
 };
-constexpr int NUM_THREADS = 512;        // 16 warps = 4 warpgroups (register rebalancing works per warpgroup)
+constexpr int NUM_THREADS = 352;        // 11 warps
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 domain: P stays below 2^8
@@ -86,6 +79,8 @@ struct FaParams {
     uint32_t idesc_qk, idesc_pv;
     int q_pairs;        // ceil(Sq / 256)
     unsigned int* work_counter;   // device-wide claim counter, zeroed before the launch
+    int stage_o;        // stage O through shared memory for coalesced stores (always when peers receive copies)
+    int tma_o;          // ... in a staging tile of its own, from which warp 10 issues one tile store per destination
     int n_peers;
     void* peer_O[MK_MAX_PEERS];
     KernelError* kerr;
@@ -193,15 +188,6 @@ __device__ __forceinline__ void exp_chunk_mixed(const uint32_t (&s)[32], float s
     }
 }
 
-// Register rebalancing between warpgroups (executed by every warp of the warpgroup, once, at start-up).
-template <int N>
-__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-// 512 threads start with 128 registers each (the whole file).  Warps 8-11 keep 56 and warps 12-15 keep 80, which frees
-// 128 * (72 + 48) = 15360; the two softmax warpgroups then take 184 each: 2 * 128 * 56 = 14336.
-constexpr int REGS_SOFTMAX = 184, REGS_CONTROL = 56, REGS_EPILOGUE = 80;
-
 // 2^x on the FMA pipes (the polynomial of exp_chunk_mixed, one value), x clamped to [-125, 125].
 __device__ __forceinline__ float poly_exp2(float x) {
     x = fminf(fmaxf(x, -125.0f), 125.0f);
@@ -299,9 +285,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sQ = smem_u32(smem), sK = sQ + SMEM_Q, sV = sK + SMEM_K;
-    uint8_t* stageO = smem + SMEM_Q + SMEM_K + SMEM_V;      // output staging: 32 rows per epilogue warp
-    float* inv_l = reinterpret_cast<float*>(stageO + TILE_BYTES);      // [2][128]: 1 / l of every row, softmax -> epilogue
-    uint64_t* bars = reinterpret_cast<uint64_t*>(inv_l + 2 * BQ);
+    uint8_t* stageO = smem + SMEM_Q + SMEM_K + SMEM_V;      // present only when p.tma_o (the launch then asks for TILE_BYTES more)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_Q + SMEM_K + SMEM_V + (p.tma_o ? TILE_BYTES : 0));
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     static_assert(NUM_BARS * 8 + 32 <= 512, "barrier area");
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -316,7 +301,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bar_ofree = bar_qempty + 8;               // [2] O_t drained by the epilogue of the previous item
     const uint32_t bar_ifull = bar_ofree + 16;               // [2] work-item slot published by the producer
     const uint32_t bar_iempty = bar_ifull + 16;              // [2] work-item slot read by every consumer
-    const uint32_t bar_oready = bar_iempty + 16;             // [2] the tile's last P is out and 1 / l published: O_t may be drained
+    const uint32_t bar_ostage_full = bar_iempty + 16;        // output staging tile written by the four warps of a query tile
+    const uint32_t bar_ostage_free = bar_ostage_full + 8;    // ... and read out by the tile stores warp 10 issued
     volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2] claimed item indices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -324,7 +310,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_qempty, 1);     // Q tiles are free once the item's last S MMA retired (one commit)
+        // Q tiles are free once the item's last S MMA retired (one commit); when the output is staged in
+        // the Q tiles, also once every softmax warp has read its staged rows back (one lane each).
+        mbar_init(bar_qempty, (p.stage_o && !p.tma_o) ? 1 + 8 : 1);
+        mbar_init(bar_ostage_full, 128);
+        mbar_init(bar_ostage_free, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(bar_kfull + 8 * i, 1);
             mbar_init(bar_kempty + 8 * i, 1);
@@ -335,17 +325,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_init(bar_sfull + 8 * t, 1);
             mbar_init(bar_pfull + 8 * t, 128);
             mbar_init(bar_pvdone + 8 * t, 1);
-            mbar_init(bar_ofree + 8 * t, 4);   // one lane per epilogue warp
-            mbar_init(bar_oready + 8 * t, 128);
+            mbar_init(bar_ofree + 8 * t, 4);   // one lane per softmax warp of the tile
             mbar_init(bar_ifull + 8 * t, 1);
-            mbar_init(bar_iempty + 8 * t, 1 + 8 + 4);    // MMA warp, eight softmax warps, four epilogue warps
+            mbar_init(bar_iempty + 8 * t, 1 + 8 + (p.tma_o ? 1 : 0));    // MMA warp, eight softmax warps, and the store warp when it takes part
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
-        for (int d = 0; d <= p.n_peers; ++d) prefetch_tensormap(&omaps.m[d]);
+        if (p.tma_o)
+            for (int d = 0; d <= p.n_peers; ++d) prefetch_tensormap(&omaps.m[d]);
     }
     if (warp == 10) {
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -362,13 +352,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // of a head first, so the CTAs running at any moment share few heads (K/V stay in L2), the
     // cheapest items come last (short tail), and the epilogue of one item overlaps the loads and
     // first MMAs of the next.  The producer publishes each claimed index through a two-slot ring.
-    // Each warpgroup adjusts its register budget as the first thing in its branch (all four warps of a warpgroup run the
-    // same instruction), so that everything the branch contains is allocated against the new limit.
-
-
-    if (warp >= 8 && warp < 12) {
-      setmaxnreg_dec<REGS_CONTROL>();
-      if (warp == 8) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer + item claims
         // Warp-uniform like the MMA issuer: all lanes run the loops and waits, lane 0 claims and copies.
         {
@@ -419,7 +403,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
         }
-      } else if (warp == 9) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
         // All 32 lanes run the loops and the waits so that descriptors and addresses stay warp-uniform;
         // one elected lane issues the tensor-core instructions.
@@ -505,9 +489,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
         }
-      }
     } else if (warp < 8) {
-        setmaxnreg_inc<REGS_SOFTMAX>();
         // ---------------------------------------------------------------- softmax / correction / epilogue
         const int t = warp >> 2;                 // query tile
         const int quarter = warp & 3;            // tensor-memory lane quarter of this warp
@@ -516,6 +498,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const uint32_t tS = tmem_base + lane_base + t * 128;
         const uint32_t tO = tmem_base + lane_base + 256 + t * 128;
         uint32_t cum = 0;                        // key blocks of this tile processed in earlier items
+        uint32_t stage_uses = 0;                 // uses of the output staging tile in earlier items (tile-store delivery)
         bool ok = true;
       for (int n = 0; ok; ++n) {
         const int slot = n & 1;
@@ -553,8 +536,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added, softcap last (which turns the
                 // -inf of masked positions into -softcap); columns past Sk do not exist and stay -inf.
                 const bool causal_here = p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset;
-                const int causal_limit = qrow + p.causal_offset;
+                const bool edge = causal_here || col0 + BKV > p.Sk;
+                const int causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
                 const float cap = p.softcap, k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
+                const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
 #pragma unroll 1
                 for (int c = 0; c < BKV / 32; ++c) {
                     uint32_t s[32];
@@ -565,16 +550,34 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         else load_mask_chunk<false>(mask_row, col0 + c * 32, p.Sk, p.mask_vec != 0, add);
                     }
                     tmem_wait_ld();
+                    if (cap > 0.0f) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int col = col0 + c * 32 + i;
-                        float x = __uint_as_float(s[i]) * p.scale;
-                        if (causal_here && col > causal_limit) x = -INFINITY;
-                        if (mask_row) x += add[i];
-                        if (cap > 0.0f) x = softcap_score(x, cap, k2);
-                        x *= LOG2E;
-                        if (col >= p.Sk) x = -INFINITY;
-                        s[i] = __float_as_uint(x);
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = col0 + c * 32 + i;
+                            float x = __uint_as_float(s[i]) * p.scale;
+                            if (edge && col > causal_limit) x = -INFINITY;
+                            if (mask_row) x += add[i];
+                            x = softcap_score(x, cap, k2) * LOG2E;
+                            if (edge && col >= p.Sk) x = -INFINITY;
+                            s[i] = __float_as_uint(x);
+                        }
+                    } else {
+                        // no cap: log2(e) * (scale * s + mask) on packed pairs; -inf (a causal or a masked position)
+                        // survives the addition either way round
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            uint64_t v = (uint64_t)s[2 * i] | ((uint64_t)s[2 * i + 1] << 32);
+                            if (mask_row) {
+                                uint64_t m2 = pack_f32x2(add[2 * i], add[2 * i + 1]);
+                                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m2) : "l"(m2), "l"(l2e2));
+                                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(sc2), "l"(m2));
+                            } else {
+                                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(sc2));
+                            }
+                            s[2 * i] = (uint32_t)v;
+                            s[2 * i + 1] = (uint32_t)(v >> 32);
+                        }
+                        if (edge) mask_chunk(s, col0 + c * 32, min(causal_limit, p.Sk - 1));
                     }
                     tmem_st_32x32b_x32(tS + c * 32, s);
                 }
@@ -665,57 +668,64 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_arrive(bar_pfull + 8 * t);
         }
 
-        // The item's last P is out: publish 1 / l for the epilogue warps and move on; they drain O_t once its last
-        // P V has retired, while these warps already work on the next item.
+        // epilogue: O / l -> global
         if (ok && nblk > 0) {
-            inv_l[t * BQ + row_in_tile] = l > 0.0f ? 1.0f / l : __int_as_float(0x7fc00000);
-            if (p.lse && qrow < p.Sq)
-                p.lse[((int64_t)batch * p.Hq + head) * p.Sq + qrow] = (l > 0.0f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
-            mbar_arrive(bar_oready + 8 * t);
+            ok = mbar_wait(bar_pvdone + 8 * t, (cum + nblk - 1) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 200000);
+            ok = __all_sync(0xffffffffu, ok);
         }
-        cum += nblk;
-      }
-    } else {
-        setmaxnreg_dec<REGS_EPILOGUE>();
-        // ---------------------------------------------------------------- epilogue: O_t / l -> 16 bit -> tile stores
-        // Follows the work items like the other consumers.  Warp w owns the 32 rows of each tile that sit in its
-        // quarter of tensor memory, and 32 rows of the staging tile (HD / 64 boxes of 32 rows x 128 bytes in the
-        // layout of a 128-byte-swizzled tile store); lane 0 issues one store per box and destination and waits for
-        // the copy engine to have read the staging rows before the warp rewrites them.
-        const int quarter = warp & 3;
-        const int row_in_tile = quarter * 32 + lane;
-        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        uint8_t* stage = stageO + quarter * (32 * HD * 2);
-        uint32_t cum[2] = {0, 0}, used[2] = {0, 0};
-        bool ok = true;
-        for (int n = 0; ok; ++n) {
-            const int slot = n & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_ifull + 8 * slot, (n >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 500000 + n));
-            if (!ok) break;
-            const int idx = item_slot[slot];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_iempty + 8 * slot);
-            if (idx >= total_items) break;
-            const WorkItem w = decode_item(p, idx);
-            for (int t = 0; t < 2 && ok; ++t) {
-                const int nblk = w.nblk[t];
-                if (nblk == 0) continue;
-                ok = mbar_wait(bar_oready + 8 * t, used[t] & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 100000 + n) &&
-                     mbar_wait(bar_pvdone + 8 * t, (cum[t] + nblk - 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 200000 + n);
+        if (ok && nblk > 0) {
+            tc_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : __int_as_float(0x7fc00000);
+            const bool in_range = qrow < p.Sq;
+            if (p.tma_o) {
+                // Head-sharded delivery: the normalised tile goes to the staging tile in the layout of a 128-byte-swizzled
+                // tile store (two boxes of 64 columns for 128-wide heads); warp 10 then issues one store per destination
+                // while these warps move on to their next item.  The staging tile serves both query tiles in turn:
+                // use u = uses of earlier items + (tile 1 after a tile 0 that had work).
+                const uint32_t u = stage_uses + ((t == 1 && w.nblk[0] > 0) ? 1u : 0u);
+                ok = mbar_wait(bar_ostage_free, (u & 1) ^ 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 900000 + n);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const float inv = inv_l[t * BQ + row_in_tile];
-                const uint32_t tO = tmem_base + lane_base + 256 + t * 128;
-                if (lane == 0) bulk_wait_group_read<0>();      // the stores of the previous tile have read this warp's staging rows
-                __syncwarp();
-#pragma unroll 1
+                if (ok) {
+    #pragma unroll 1
+                    for (int c = 0; c < HD / 32; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(tO + c * 32, r);
+                        tmem_wait_ld();
+                        uint32_t pk[16];
+    #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
+                            if constexpr (BF16) {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                            } else {
+                                __half2 h = __floats2half2_rn(a, b);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        }
+                        uint8_t* box = stageO + (c >> 1) * HALF_BYTES + row_in_tile * 128;     // 64-column box c / 2, this thread's row
+    #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<uint4*>(box + ((((c & 1) * 4 + i) ^ (row_in_tile & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    }
+                    tc_fence_before();
+                    fence_proxy_async_smem();           // the staged rows become visible to the copy engine
+                    mbar_arrive(bar_ostage_full);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
+                }
+            } else if (p.stage_o) {
+                // The Q tile's shared memory is free once the last MMA of this tile has retired: stage the
+                // normalised output there (16-byte pieces XOR-swizzled by row) so that the global stores
+                // -- local and to peer GPUs -- go out as whole rows (2 HD contiguous bytes) per group of lanes.
+                uint8_t* stage = smem + t * TILE_BYTES;
+    #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(tO + c * 32, r);
                     tmem_wait_ld();
                     uint32_t pk[16];
-#pragma unroll
+    #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
                         if constexpr (BF16) {
@@ -726,27 +736,104 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             pk[i] = *reinterpret_cast<uint32_t*>(&h);
                         }
                     }
-                    uint8_t* box = stage + (c >> 1) * 4096 + lane * 128;      // 64-column box c / 2, this thread's row
-#pragma unroll
+    #pragma unroll
                     for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4*>(box + ((((c & 1) * 4 + i) ^ (lane & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                        *reinterpret_cast<uint4*>(stage + row_in_tile * (HD * 2) + (((c * 4 + i) ^ (row_in_tile & (HD / 8 - 1))) << 4)) =
+                            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
                 }
                 tc_fence_before();
-                fence_proxy_async_smem();           // the staged rows become visible to the copy engine
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
-                    const int y = w.q0 + t * BQ + quarter * 32;
-                    if (y < p.Sq) {
-                        const uint32_t src = smem_u32(stage);
-#pragma unroll
-                        for (int h = 0; h < NH; ++h)
-                            for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * 4096, h * 64, y, w.head, w.batch);
-                    }
-                    bulk_commit_group();
+                __syncwarp();   // each warp reads back only the 32 rows it wrote
+                if (lane == 0) mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
+                const int64_t head_off = batch * p.o_strides[0] + head * p.o_strides[1];
+                constexpr int LPR = HD / 8;              // lanes (16-byte pieces) per output row
+    #pragma unroll 4
+                for (int it = 0; it < LPR; ++it) {
+                    const int rr = quarter * 32 + it * (32 / LPR) + lane / LPR, ch = lane % LPR;
+                    const int grow = q0 + t * BQ + rr;
+                    if (grow >= p.Sq) continue;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (HD * 2) + ((ch ^ (rr & (LPR - 1))) << 4));
+                    const int64_t off = head_off + (int64_t)grow * p.o_strides[2] + ch * 8;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) + off) = v;
+                    for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.peer_O[q]) + off) = v;
                 }
-                cum[t] += nblk;
-                used[t] += 1;
+            } else {   // single GPU: every thread stores its own row directly
+                const int64_t off = batch * p.o_strides[0] + head * p.o_strides[1] + (int64_t)qrow * p.o_strides[2];
+    #pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tO + c * 32, r);
+                    tmem_wait_ld();
+                    uint32_t pk[16];
+    #pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
+                        if constexpr (BF16) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                            pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __floats2half2_rn(a, b);
+                            pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    if (in_range) {
+                        uint16_t* dst = reinterpret_cast<uint16_t*>(p.O) + off + c * 32;
+    #pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_ofree + 8 * t);
+            }
+            if (p.lse && in_range)
+                p.lse[((int64_t)batch * p.Hq + head) * p.Sq + qrow] = (l > 0.0f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        }
+        stage_uses += (w.nblk[0] > 0 ? 1u : 0u) + (w.nblk[1] > 0 ? 1u : 0u);
+        if (p.stage_o && !p.tma_o) {            // the staging area (this item's Q tile) has been read back
+            // A tile without work must not release the Q tiles of item n before item n-1's phase of the
+            // barrier has completed; this item's Q having landed proves that it has.
+            if (nblk == 0) {
+                ok = mbar_wait(bar_q, n & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 800000 + n);
+                ok = __all_sync(0xffffffffu, ok);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_qempty);
+        }
+        cum += nblk;
+      }
+    }
+
+    else if (warp == 10 && p.tma_o) {
+        // ---------------------------------------------------------------- tile stores of finished output tiles
+        // Follows the work items like every other consumer; for each query tile that had work it waits until the four
+        // softmax warps have staged the tile, issues one tile store per 64-column box and destination (the local O and
+        // every peer's O over NVLink), and frees the staging tile once the copy engine has read it.
+        uint32_t u = 0;
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+            const int slot = n & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_ifull + 8 * slot, (n >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 500000 + n));
+            if (!ok) break;
+            const int idx = __reduce_max_sync(0xffffffffu, (int)item_slot[slot]);
+            if (lane == 0) mbar_arrive(bar_iempty + 8 * slot);
+            if (idx >= total_items) break;
+            const WorkItem w = decode_item(p, idx);
+            for (int t = 0; t < 2 && ok; ++t) {
+                if (w.nblk[t] == 0) continue;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_ostage_full, u & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, n));
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t src = smem_u32(stageO);
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+                        for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * HALF_BYTES, h * 64, w.q0 + t * BQ, w.head, w.batch);
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(bar_ostage_free);
+                }
+                __syncwarp();
+                ++u;
             }
         }
         if (lane == 0) bulk_wait_group<0>();     // every tile store has completed before the CTA may leave
@@ -763,13 +850,13 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// [B, H, S, D] tensor with element strides (batch, head, row); box = 64 columns x box_rows rows.
-mk_status encode_bhsd(CUtensorMap* map, int dtype, const void* base, int B, int H, int S, int D, const int64_t* strides, uint32_t box_rows = 128) {
+// [B, H, S, D] tensor with element strides (batch, head, row); box = 64 columns x 128 rows.
+mk_status encode_bhsd(CUtensorMap* map, int dtype, const void* base, int B, int H, int S, int D, const int64_t* strides) {
     static PFN_encodeTiled encode = (PFN_encodeTiled)driver_entry("cuTensorMapEncodeTiled");
     if (!encode) return fail(MK_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable (driver too old?)");
     cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
     cuuint64_t str[3] = {(cuuint64_t)strides[2] * 2, (cuuint64_t)strides[1] * 2, (cuuint64_t)strides[0] * 2};
-    cuuint32_t box[4] = {64, box_rows, 1, 1};
+    cuuint32_t box[4] = {64, 128, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = encode(map, dtype == MK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                         const_cast<void*>(base), dims, str, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -788,7 +875,11 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     *handled = false;
     if (dev->prop.major != 10) return MK_OK;
     if (d.dtype != MK_BF16 && d.dtype != MK_F16) return MK_OK;
-    if (d.D != d.Dv || (d.D != 128 && d.D != 64)) return MK_OK;
+    // Head sizes: the kernel is built for 64 and 128 columns; any head size that is a multiple of 8 (16-byte rows) up to 128
+    // runs on the next larger one -- the tile loads zero-fill the columns past D (zero products in Q K^T, zero
+    // columns of O) and the stores of O drop them.
+    if (d.D != d.Dv || d.D % 8 != 0 || d.D < 8 || d.D > 128) return MK_OK;
+    const int HDk = d.D <= 64 ? 64 : 128;
     if (d.Sk <= 0 || d.Sq <= 0) return MK_OK;
     if (d.causal && d.causal_offset < 0) return MK_OK;   // rows without any visible key (NaN rows) are the general kernel's business
     if (!strides_ok(d.q_strides, d.D) || !strides_ok(d.k_strides, d.D) || !strides_ok(d.v_strides, d.D)) return MK_OK;
@@ -837,13 +928,20 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     for (int i = 0; i < 3; ++i) p.o_strides[i] = d.o_strides[i];
     const uint32_t fmt = d.dtype == MK_BF16 ? 1u : 0u;
     p.idesc_qk = idesc_f16(fmt, 0u, 0u, BQ, BKV);
-    p.idesc_pv = idesc_f16(fmt, 0u, 1u, BQ, (uint32_t)d.D);
+    p.idesc_pv = idesc_f16(fmt, 0u, 1u, BQ, (uint32_t)HDk);
     p.q_pairs = (int)q_pairs;
-    // the output leaves through tile stores of 32-row boxes: one map per destination
+    p.stage_o = d.n_peers > 0 || getenv("MOROK_B200_ATTN_STAGE_O") != nullptr;
+    // peers receive their copies as tile stores issued from a staging tile (MOROK_B200_PEER_TMA=0: as 16-byte stores
+    // of the softmax warps out of the item's Q tile, the older path)
+    static const bool peer_tma = [] { const char* e = getenv("MOROK_B200_PEER_TMA"); return e ? atoi(e) != 0 : true; }();
+    // ... and for head sizes the kernel pads to 64 / 128 columns: the tile store drops the padding columns
+    p.tma_o = (d.n_peers > 0 && peer_tma) || d.D != HDk || getenv("MOROK_B200_ATTN_TMA_O") != nullptr;
     alignas(64) OStoreMaps omaps{};
-    for (int i = 0; i <= d.n_peers; ++i) {
-        s1 = encode_bhsd(&omaps.m[i], d.dtype, i == 0 ? d.O : d.peer_O[i - 1], d.B, d.Hq, d.Sq, d.Dv, d.o_strides, 32);
-        if (s1 != MK_OK) return s1;
+    if (p.tma_o) {
+        for (int i = 0; i <= d.n_peers; ++i) {
+            s1 = encode_bhsd(&omaps.m[i], d.dtype, i == 0 ? d.O : d.peer_O[i - 1], d.B, d.Hq, d.Sq, d.Dv, d.o_strides);
+            if (s1 != MK_OK) return s1;
+        }
     }
     p.n_peers = d.n_peers;
     for (int i = 0; i < d.n_peers; ++i) p.peer_O[i] = d.peer_O[i];
@@ -861,9 +959,9 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
         return cudaSuccess;
     };
     const bool bf = d.dtype == MK_BF16;
-    const int smem128 = Cfg<128>::SMEM_BYTES, smem64 = Cfg<64>::SMEM_BYTES;
+    const int smem128 = p.tma_o ? Cfg<128>::SMEM_BYTES_DELIVER : Cfg<128>::SMEM_BYTES, smem64 = p.tma_o ? Cfg<64>::SMEM_BYTES_DELIVER : Cfg<64>::SMEM_BYTES;
 #define MK_FA(BF, HD_, GEN, SMEM) MK_CUDA(launch(sdpa_tc_kernel<BF, HD_, GEN>, SMEM))
-    if (d.D == 128) {
+    if (HDk == 128) {
         if (general) { if (bf) MK_FA(true, 128, true, smem128); else MK_FA(false, 128, true, smem128); }
         else { if (bf) MK_FA(true, 128, false, smem128); else MK_FA(false, 128, false, smem128); }
     } else {
@@ -872,7 +970,7 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     }
 #undef MK_FA
     MK_CUDA(cudaGetLastError());
-    note_launch(dev, st, d.D == 128 ? (general ? "sdpa_tc_d128_general" : "sdpa_tc_d128") : (general ? "sdpa_tc_d64_general" : "sdpa_tc_d64"));
+    note_launch(dev, st, HDk == 128 ? (general ? "sdpa_tc_d128_general" : "sdpa_tc_d128") : (general ? "sdpa_tc_d64_general" : "sdpa_tc_d64"));
     *handled = true;
     return MK_OK;
 }

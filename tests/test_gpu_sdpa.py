@@ -357,3 +357,26 @@ def test_tensor_api_takes_broadcast_and_bool_masks(dev):
     assert_close(orc.bf16_to_f32(out.as_ndarray()), orc.sdpa_f32(q, k, v, mask=add), mk.MK_BF16, "additive [Sq, Sk] mask")
     with pytest.raises(mk.MorokError):       # a mask that does not broadcast is refused when the graph is built
         T(q).scaled_dot_product_attention(T(k), T(v), attn_mask=Tensor.from_ndarray(dev, np.zeros((3, S, S), np.float32)))
+
+
+@pytest.mark.parametrize("D", [32, 80, 96, 120])
+@pytest.mark.parametrize("case", [(1, 2, 2, 256, 256, True), (2, 4, 2, 200, 333, False)])
+def test_other_head_sizes_run_on_the_tensor_core_kernel(dev, case, D):
+    """Head sizes between the two the kernel is built for (64, 128) run on the next larger one: the tile loads
+    zero-fill the missing columns and the tile stores drop them.  The reference is generic in the head size
+    (tensor/src/transformer.rs:88-96; scale 1 / sqrt(D) of the real D)."""
+    B, H, Hkv, Sq, Sk, causal = case
+    rng = np.random.default_rng(D + Sq)
+    q, k, v = (orc.round_bf16(rng.standard_normal(s, dtype=np.float32)) for s in ((B, H, Sq, D), (B, Hkv, Sk, D), (B, Hkv, Sk, D)))
+    Q, K, V = (dev.from_numpy(orc.f32_to_bf16(t)) for t in (q, k, v))
+    O = dev.from_numpy(np.full((B, H, Sq, D), 0xFFFF, np.uint16))
+    guard = dev.from_numpy(np.full(4096, 0xABCD, np.uint16))       # something right behind O that must stay untouched
+    dev.profile_begin()
+    dev.sdpa(Q, K, V, O, B, H, Hkv, Sq, Sk, D, dtype=mk.MK_BF16, causal=causal)
+    launched = [n for n, _ in dev.profile_end()]
+    assert launched == [f"sdpa_tc_d{64 if D <= 64 else 128}"], launched
+    assert dev.kernel_status() == 0
+    got_bits = O.copyout(np.uint16, (B, H, Sq, D))
+    assert not np.any(got_bits == 0xFFFF)
+    assert np.all(guard.copyout(np.uint16, (4096,)) == 0xABCD)
+    assert_close(orc.bf16_to_f32(got_bits), orc.sdpa_f32(q, k, v, causal=causal), mk.MK_BF16, f"D={D} {case}")
