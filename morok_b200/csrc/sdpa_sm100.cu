@@ -531,29 +531,25 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const int col_limit = p.causal ? min(p.Sk - 1, qrow + p.causal_offset) : p.Sk - 1;   // last visible column of this row
             const float sc = GENERAL ? 1.0f : p.scale_log2;     // the general form leaves log2-domain scores in tensor memory
 
+            // Pass 1: the row maximum.  The 128 scores are only reduced here and die at once, so the
+            // exponentiation below never competes with a whole row for registers.
+            float mx;
             if constexpr (GENERAL) {
-                // Scores -> log2(e) * softcap(scale * s, causal rule, mask), in place.  Order as in the reference
-                // (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added, softcap last (which turns the
-                // -inf of masked positions into -softcap); columns past Sk do not exist and stay -inf.
+                // General form: this pass also rewrites the scores in place as log2(e) * softcap(scale * s, causal rule,
+                // mask).  Order as in the reference (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added,
+                // softcap last (which turns the -inf of masked positions into -softcap); columns past Sk do not
+                // exist and stay -inf.  Two halves of 64 columns, both loads and the mask reads of a half in flight.
                 const bool causal_here = p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset;
                 const bool edge = causal_here || col0 + BKV > p.Sk;
                 const int causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
                 const float cap = p.softcap, k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
                 const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
-#pragma unroll 1
-                for (int c = 0; c < BKV / 32; ++c) {
-                    uint32_t s[32];
-                    tmem_ld_32x32b_x32(tS + c * 32, s);
-                    float add[32];
-                    if (mask_row) {
-                        if (p.mask_bool) load_mask_chunk<true>(mask_row, col0 + c * 32, p.Sk, p.mask_vec != 0, add);
-                        else load_mask_chunk<false>(mask_row, col0 + c * 32, p.Sk, p.mask_vec != 0, add);
-                    }
-                    tmem_wait_ld();
+                mx = -INFINITY;
+                auto transform = [&](uint32_t (&s)[32], const float (&add)[32], int cbase) {
                     if (cap > 0.0f) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int col = col0 + c * 32 + i;
+                            const int col = cbase + i;
                             float x = __uint_as_float(s[i]) * p.scale;
                             if (edge && col > causal_limit) x = -INFINITY;
                             if (mask_row) x += add[i];
@@ -577,17 +573,31 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             s[2 * i] = (uint32_t)v;
                             s[2 * i + 1] = (uint32_t)(v >> 32);
                         }
-                        if (edge) mask_chunk(s, col0 + c * 32, min(causal_limit, p.Sk - 1));
+                        if (edge) mask_chunk(s, cbase, min(causal_limit, p.Sk - 1));
                     }
-                    tmem_st_32x32b_x32(tS + c * 32, s);
+                };
+#pragma unroll 1
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t sa[32], sb[32];
+                    tmem_ld_32x32b_x32(tS + half * 64, sa);
+                    tmem_ld_32x32b_x32(tS + half * 64 + 32, sb);
+                    float add[32];       // one chunk of mask values at a time (registers); the second read hits the same lines
+                    auto load_add = [&](int cbase) {
+                        if (!mask_row) return;
+                        if (p.mask_bool) load_mask_chunk<true>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+                        else load_mask_chunk<false>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+                    };
+                    load_add(col0 + half * 64);
+                    tmem_wait_ld();
+                    transform(sa, add, col0 + half * 64);
+                    load_add(col0 + half * 64 + 32);
+                    transform(sb, add, col0 + half * 64 + 32);
+                    mx = fmaxf(mx, fmaxf(max_chunk(sa), max_chunk(sb)));
+                    tmem_st_32x32b_x32(tS + half * 64, sa);
+                    tmem_st_32x32b_x32(tS + half * 64 + 32, sb);
                 }
                 tmem_wait_st();
-            }
-
-            // Pass 1: the row maximum.  The 128 scores are only reduced here and die at once, so the
-            // exponentiation below never competes with a whole row for registers.
-            float mx;
-            {
+            } else {
                 uint32_t s0[32], s1[32], s2[32], s3[32];
                 tmem_ld_32x32b_x32(tS, s0);
                 tmem_ld_32x32b_x32(tS + 32, s1);
