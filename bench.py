@@ -184,18 +184,29 @@ def run_ours(args, rank, world, local_rank, dist):
     B, H, S, D = cfg["attn"]
     col0, Nl = sharding.gemm_column_shard(N, rank, world)      # this rank's columns of B and C
     h0, Hl, _, _ = sharding.head_shard(H, H, rank, world)      # ... and its heads
-    check = world > 1 and not args.no_delivery_check           # the check needs the inputs on the host as well
+    check = world > 1 and not args.no_delivery_check
 
-    def tensor(shape, sigma, seed, keep):
-        n = int(np.prod(shape))
-        buf = dev.alloc(n * 2)
-        # a development run that skips the delivery check repeats one random chunk instead of drawing every element
-        host = synth.fill_normal_bf16(dev, buf, n, sigma, seed, keep_host=keep, tile=(world > 1 and not check))
-        return buf, (host.reshape(shape) if host is not None else None)
-
-    A, A_host = tensor((M, K), 1.0, 1, check)
-    Bw, B_host = tensor((K, N), 0.02, 2, check)                # full B; this rank reads its column block in place
-    (Q, Q_host), (Kt, K_host), (V, V_host) = (tensor((B, H, S, D), 1.0, 3 + i, check) for i in range(3))
+    # Inputs.  Every tensor is drawn chunk by chunk, each chunk from its own generator (seed, chunk index): A in
+    # blocks of 64 rows, B in panels of 128 columns, Q / K / V per (batch, head).  A rank draws what it reads -- all
+    # of A, its column block of B, its heads -- and the delivery check later re-draws the pieces it samples.
+    SEED_A, SEED_B, SEED_Q = 1, 2, 3
+    assert col0 % synth.COL_PANEL == 0 and Nl % synth.COL_PANEL == 0, "column shards are whole panels of the generator"
+    A = dev.alloc(M * K * 2)
+    for r in range(0, M, 2048):
+        rows = min(2048, M - r)
+        A.view(r * K * 2, rows * K * 2).copyin(synth.matrix_rows_bf16(SEED_A, K, r, rows, 1.0))
+    Bw = dev.alloc(K * N * 2)                                   # full-size B; this rank fills and reads its column block in place
+    shard = dev.from_numpy(synth.matrix_panels_bf16(SEED_B, K, col0, Nl, 0.02))
+    dst = (C.c_void_p * 1)(Bw.ptr)
+    mk._ffi.check(dev.lib.mk_all_gather_push_2d(dev.h, None, shard.ptr, Nl * 2, Nl * 2, K, dst, 1, col0 * 2, N * 2))
+    dev.sync()
+    shard.free()
+    Q, Kt, V = (dev.alloc(B * H * S * D * 2) for _ in range(3))
+    for i, t in enumerate((Q, Kt, V)):
+        for b in range(B):
+            heads = np.stack([synth.head_slice_bf16(SEED_Q + i, H, b, h, S, D) for h in range(h0, h0 + Hl)])
+            t.view((b * H + h0) * S * D * 2, Hl * S * D * 2).copyin(heads)
+    dev.sync()
     Cfull = dev.alloc(M * N * 2)
     Ofull = dev.alloc(B * H * S * D * 2)
 
@@ -401,7 +412,7 @@ def run_ours(args, rank, world, local_rank, dist):
                                                          dict(M=M, Nl=Nl, B=B, Hl=Hl, S=S, D=D), fl_gemm + fl_attn)
         if check:
             result["delivery_check"] = delivery_check(mk, dev, stream, dist, local_rank, rank, world, step, barrier, Cfull, Ofull,
-                                                      dict(M=M, K=K, N=N, B=B, H=H, S=S, D=D), A_host, B_host, Q_host, K_host, V_host)
+                                                      dict(M=M, K=K, N=N, B=B, H=H, S=S, D=D), (SEED_A, SEED_B, SEED_Q))
 
     sampler.stop()
     result["clocks"] = sampler.region(t_begin, t_end)
@@ -537,16 +548,18 @@ def nccl_leg(mk, dev, stream, dist, local_rank, world, gemm, attn, timed, n_side
             "note": "kernels without delivery + ncclAllGather of the C and O shards (gather of C overlaps attention); gathered as [g][shard]"}
 
 
-def delivery_check(mk, dev, stream, dist, local_rank, rank, world, step, barrier, Cfull, Ofull, s, A_host, B_host, Q_host, K_host, V_host):
+def delivery_check(mk, dev, stream, dist, local_rank, rank, world, step, barrier, Cfull, Ofull, s, seeds):
     """Correctness of what the peers delivered.  C and O are filled with a poison pattern on every rank, one
     delivered step runs, and every rank compares -- for EVERY rank's column block of C and head slice of O as
-    they now stand in ITS OWN buffers -- sampled rows / heads with the CPU oracle (the checker; outside any
-    timed region).  Pass / fail is reduced over the ranks."""
+    they now stand in ITS OWN buffers -- sampled rows / column panels / heads with the CPU oracle (the checker;
+    outside any timed region), on inputs re-drawn from the generators' chunk seeds.  Pass / fail is reduced over
+    the ranks."""
     import torch
-    from morok_b200 import sharding
+    from morok_b200 import sharding, synth
     from oracle import oracle as orc
     orc.lib().orc_set_threads(max(1, (os.cpu_count() or 1) // world))       # torchrun exports OMP_NUM_THREADS=1
     M, K, N, B, H, S, D = (s[k] for k in ("M", "K", "N", "B", "H", "S", "D"))
+    seed_a, seed_b, seed_q = seeds
     for buf, nbytes in ((Cfull, M * N * 2), (Ofull, B * H * S * D * 2)):
         mk._ffi.check(dev.lib.mk_memset_async(dev.h, buf.ptr, 0xFF, nbytes, stream.h))
     barrier()                           # poison is in place everywhere before anyone stores
@@ -556,27 +569,34 @@ def delivery_check(mk, dev, stream, dist, local_rank, rank, world, step, barrier
     rng = np.random.default_rng(1234)   # the same sample on every rank
     rows = np.unique(np.concatenate([[0, 255, 256, 8191, 8192, M - 257, M - 256, M - 1], rng.integers(0, M, 12)]))
     failures, n_rows, n_heads, worst = [], 0, 0, 0.0
-    a_rows = bf(A_host[rows])
+    a_rows = bf(np.concatenate([synth.matrix_rows_bf16(seed_a, K, int(r), 1, 1.0) for r in rows]))
     c_rows = np.stack([Cfull.view(int(r) * N * 2, N * 2).copyout(np.uint16, (N,)) for r in rows])
+    P = synth.COL_PANEL
     for r in range(world):
         c0, nc = sharding.gemm_column_shard(N, r, world)
-        ref = orc.matmul_f32(a_rows, bf(np.ascontiguousarray(B_host[:, c0:c0 + nc])))
-        got_bits = c_rows[:, c0:c0 + nc]
-        got = bf(got_bits)
-        bad = (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)) | (got_bits == 0xFFFF)
-        worst = max(worst, float(np.max(np.abs(got - ref) / (1e-2 + 2e-2 * np.abs(ref)))))
+        # the first, the last and one random panel of 128 columns of this rank's block: tile seams and the block's edges
+        panels = sorted({c0 // P, (c0 + nc) // P - 1, c0 // P + int(rng.integers(0, nc // P))})
+        for pidx in panels:
+            ref = orc.matmul_f32(a_rows, bf(synth.matrix_panels_bf16(seed_b, K, pidx * P, P, 0.02)))
+            got_bits = c_rows[:, pidx * P:(pidx + 1) * P]
+            got = bf(got_bits)
+            bad = (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)) | (got_bits == 0xFFFF)
+            worst = max(worst, float(np.max(np.abs(got - ref) / (1e-2 + 2e-2 * np.abs(ref)))))
+            if bad.any():
+                failures.append(f"rank {rank}: C columns {pidx * P}..{pidx * P + P - 1} (rank {r}'s block): {int(bad.sum())} of {bad.size} sampled elements off")
+        # poison anywhere in the sampled rows of this block means a tile was never delivered
+        if np.any(c_rows[:, c0:c0 + nc] == 0xFFFF):
+            failures.append(f"rank {rank}: poison left in rank {r}'s column block of C")
         n_rows += len(rows)
-        if bad.any():
-            failures.append(f"rank {rank}: C columns of rank {r}: {int(bad.sum())} of {bad.size} sampled elements off")
     row_blocks = [(0, 64), (S // 2 - 32, 64), (S - 64, 64)]     # per head: first rows, a tile seam in the middle, the last rows
     for r in range(world):
         q0, nq, _, _ = sharding.head_shard(H, H, r, world)
         for (b, h) in ((int(rng.integers(0, B)), q0), (int(rng.integers(0, B)), q0 + nq - 1)):
+            qh, kh, vh = (bf(synth.head_slice_bf16(seed_q + i, H, b, h, S, D)) for i in range(3))
             for (r0, nr) in row_blocks:
                 off = ((b * H + h) * S + r0) * D * 2
                 got_bits = Ofull.view(off, nr * D * 2).copyout(np.uint16, (nr, D))
-                ref = orc.sdpa_f32(bf(Q_host[b:b + 1, h:h + 1, r0:r0 + nr]), bf(K_host[b:b + 1, h:h + 1, :r0 + nr]),
-                                   bf(V_host[b:b + 1, h:h + 1, :r0 + nr]), causal=True, causal_offset=r0)[0, 0]
+                ref = orc.sdpa_f32(qh[None, None, r0:r0 + nr], kh[None, None, :r0 + nr], vh[None, None, :r0 + nr], causal=True, causal_offset=r0)[0, 0]
                 got = bf(got_bits)
                 bad = (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)) | (got_bits == 0xFFFF)
                 worst = max(worst, float(np.max(np.abs(got - ref) / (1e-2 + 2e-2 * np.abs(ref)))))
@@ -589,9 +609,9 @@ def delivery_check(mk, dev, stream, dist, local_rank, rank, world, step, barrier
     dist.all_gather_object(all_fail, failures[:4])
     return {"ok": bool(ok.item() == 1), "rows": n_rows, "heads": n_heads, "ranks": world,
             "worst_error_over_bar": round(worst, 3),
-            "what": "after a poison fill and one delivered step, every rank checked sampled rows of every rank's column block of C "
-                    "and two heads (three 64-row blocks each) of every rank's slice of O, as delivered into its own buffers, against "
-                    "the CPU oracle at 2e-2 rel + 1e-2 abs; poison left behind counts as a failure",
+            "what": "after a poison fill and one delivered step, every rank checked, in its own buffers, sampled rows of every rank's column "
+                    "block of C (first, last and a random 128-column panel against the oracle; no poison anywhere in those rows) and two heads "
+                    "(three 64-row blocks each) of every rank's slice of O, at 2e-2 rel + 1e-2 abs",
             "failures": [f for fs in all_fail for f in (fs or [])][:8]}
 
 

@@ -1,4 +1,5 @@
-// Fused attention forward for head sizes 128 and 64 on Blackwell tensor cores (sm_100a).
+// Fused attention forward on Blackwell tensor cores (sm_100a): head sizes up to 128 (built for 64 and 128 columns;
+// other multiples of 8 run zero-padded on the next larger one).
 //
 // One kernel replaces the >= 5 kernels (and the materialised [Sq,Sk] score matrix) that morok
 // schedules for `scaled_dot_product_attention` (tensor/src/transformer.rs:78-137):
@@ -12,17 +13,22 @@
 //                    exp2 (three pairs in four on the special-function unit, the fourth as a
 //                    polynomial on the FMA pipes), P (16 bit) written back over S, m and l in
 //                    registers; O is rescaled only when the maximum moved by > 2^8; finally O is
-//                    normalised and stored (128-bit stores, also to peer GPUs)
+//                    normalised and stored -- 128-bit stores of each thread's row, or, when peer GPUs
+//                    receive copies (head-sharded runs) or the head size is padded, into a staging tile
 //   warp 8           TMA producer: claims work items, Q per item, then K / V blocks of 128 keys
 //                    through a ring that runs on across items
 //   warp 9           MMA issuer: S_t = Q_t K^T and O_t += P_t V, tile 0 and tile 1 interleaved so the
 //                    tensor pipe works on one tile while the other is in softmax.  All 32 lanes run
 //                    the loops and waits (descriptors then live in uniform registers); one elected
 //                    lane is predicated on the tcgen05 instructions
-//   warp 10          tensor-memory allocation (512 columns: S0 S1 at 0 / 128, O0 O1 at 256 / 384)
+//   warp 10          tensor-memory allocation (512 columns: S0 S1 at 0 / 128, O0 O1 at 256 / 384); then, for
+//                    staged output, one tile store per destination (local O and every peer's O over
+//                    NVLink) of each staged tile
 //
 // K is a K-major B operand, V an MN-major one (read as stored, no transpose), P is the A operand
 // taken from tensor memory.  Key blocks entirely above the causal diagonal are never loaded.
+// A mask (additive or bool, any shape that broadcasts against the scores) and a softcap run in the same
+// kernel: its general form rewrites the scores in tensor memory during the row-maximum pass.
 // All barrier waits are bounded; a wait that gives up records a code in the device error word.
 #include <cstdlib>
 
@@ -79,8 +85,8 @@ struct FaParams {
     uint32_t idesc_qk, idesc_pv;
     int q_pairs;        // ceil(Sq / 256)
     unsigned int* work_counter;   // device-wide claim counter, zeroed before the launch
-    int stage_o;        // stage O through shared memory for coalesced stores (always when peers receive copies)
-    int tma_o;          // ... in a staging tile of its own, from which warp 10 issues one tile store per destination
+    int tma_o;          // stage O in a tile of shared memory from which warp 10 issues one tile store per destination
+                        // (always when peers receive copies, and for head sizes the kernel pads)
     int n_peers;
     void* peer_O[MK_MAX_PEERS];
     KernelError* kerr;
@@ -297,7 +303,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bar_sfull = bar_vempty + 8 * KV_STAGES;   // [2] S_t written by the tensor core
     const uint32_t bar_pfull = bar_sfull + 16;               // [2] P_t written (and O_t rescaled) by the softmax warps
     const uint32_t bar_pvdone = bar_pfull + 16;              // [2] O_t += P_t V retired
-    const uint32_t bar_qempty = bar_pvdone + 16;             // Q tiles may be overwritten (last S issued, staging done)
+    const uint32_t bar_qempty = bar_pvdone + 16;             // Q tiles may be overwritten (the item's last S MMA was issued)
     const uint32_t bar_ofree = bar_qempty + 8;               // [2] O_t drained by the epilogue of the previous item
     const uint32_t bar_ifull = bar_ofree + 16;               // [2] work-item slot published by the producer
     const uint32_t bar_iempty = bar_ifull + 16;              // [2] work-item slot read by every consumer
@@ -310,9 +316,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        // Q tiles are free once the item's last S MMA retired (one commit); when the output is staged in
-        // the Q tiles, also once every softmax warp has read its staged rows back (one lane each).
-        mbar_init(bar_qempty, (p.stage_o && !p.tma_o) ? 1 + 8 : 1);
+        mbar_init(bar_qempty, 1);     // Q tiles are free once the item's last S MMA retired (one commit)
         mbar_init(bar_ostage_full, 128);
         mbar_init(bar_ostage_free, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
@@ -724,49 +728,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
                 }
-            } else if (p.stage_o) {
-                // The Q tile's shared memory is free once the last MMA of this tile has retired: stage the
-                // normalised output there (16-byte pieces XOR-swizzled by row) so that the global stores
-                // -- local and to peer GPUs -- go out as whole rows (2 HD contiguous bytes) per group of lanes.
-                uint8_t* stage = smem + t * TILE_BYTES;
-    #pragma unroll 1
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(tO + c * 32, r);
-                    tmem_wait_ld();
-                    uint32_t pk[16];
-    #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
-                        if constexpr (BF16) {
-                            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                            pk[i] = *reinterpret_cast<uint32_t*>(&h);
-                        } else {
-                            __half2 h = __floats2half2_rn(a, b);
-                            pk[i] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                    }
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        *reinterpret_cast<uint4*>(stage + row_in_tile * (HD * 2) + (((c * 4 + i) ^ (row_in_tile & (HD / 8 - 1))) << 4)) =
-                            make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-                }
-                tc_fence_before();
-                __syncwarp();   // each warp reads back only the 32 rows it wrote
-                if (lane == 0) mbar_arrive(bar_ofree + 8 * t);   // O_t is in shared memory now: the next item may overwrite it
-                const int64_t head_off = batch * p.o_strides[0] + head * p.o_strides[1];
-                constexpr int LPR = HD / 8;              // lanes (16-byte pieces) per output row
-    #pragma unroll 4
-                for (int it = 0; it < LPR; ++it) {
-                    const int rr = quarter * 32 + it * (32 / LPR) + lane / LPR, ch = lane % LPR;
-                    const int grow = q0 + t * BQ + rr;
-                    if (grow >= p.Sq) continue;
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * (HD * 2) + ((ch ^ (rr & (LPR - 1))) << 4));
-                    const int64_t off = head_off + (int64_t)grow * p.o_strides[2] + ch * 8;
-                    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.O) + off) = v;
-                    for (int q = 0; q < p.n_peers; ++q) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.peer_O[q]) + off) = v;
-                }
-            } else {   // single GPU: every thread stores its own row directly
+            } else {   // every thread stores its own row directly
                 const int64_t off = batch * p.o_strides[0] + head * p.o_strides[1] + (int64_t)qrow * p.o_strides[2];
     #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
@@ -800,16 +762,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 p.lse[((int64_t)batch * p.Hq + head) * p.Sq + qrow] = (l > 0.0f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
         }
         stage_uses += (w.nblk[0] > 0 ? 1u : 0u) + (w.nblk[1] > 0 ? 1u : 0u);
-        if (p.stage_o && !p.tma_o) {            // the staging area (this item's Q tile) has been read back
-            // A tile without work must not release the Q tiles of item n before item n-1's phase of the
-            // barrier has completed; this item's Q having landed proves that it has.
-            if (nblk == 0) {
-                ok = mbar_wait(bar_q, n & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 800000 + n);
-                ok = __all_sync(0xffffffffu, ok);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_qempty);
-        }
         cum += nblk;
       }
     }
@@ -940,12 +892,10 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     p.idesc_qk = idesc_f16(fmt, 0u, 0u, BQ, BKV);
     p.idesc_pv = idesc_f16(fmt, 0u, 1u, BQ, (uint32_t)HDk);
     p.q_pairs = (int)q_pairs;
-    p.stage_o = d.n_peers > 0 || getenv("MOROK_B200_ATTN_STAGE_O") != nullptr;
-    // peers receive their copies as tile stores issued from a staging tile (MOROK_B200_PEER_TMA=0: as 16-byte stores
-    // of the softmax warps out of the item's Q tile, the older path)
-    static const bool peer_tma = [] { const char* e = getenv("MOROK_B200_PEER_TMA"); return e ? atoi(e) != 0 : true; }();
+    // Peers receive their copies as tile stores issued from a staging tile; without peers every thread stores its
+    // own row (MOROK_B200_ATTN_TMA_O forces the staged form for measurements).
     // ... and for head sizes the kernel pads to 64 / 128 columns: the tile store drops the padding columns
-    p.tma_o = (d.n_peers > 0 && peer_tma) || d.D != HDk || getenv("MOROK_B200_ATTN_TMA_O") != nullptr;
+    p.tma_o = d.n_peers > 0 || d.D != HDk || getenv("MOROK_B200_ATTN_TMA_O") != nullptr;
     alignas(64) OStoreMaps omaps{};
     if (p.tma_o) {
         for (int i = 0; i <= d.n_peers; ++i) {

@@ -50,3 +50,45 @@ def fill_normal_bf16(dev, buf, n: int, sigma: float, seed: int, chunk: int = 1 <
         off += m
     dev.sync()
     return host
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Chunk-seeded tensors: every chunk of a tensor has its own generator, seeded by (seed, chunk index), so that a
+# process can draw exactly the part it owns -- and any other part later, to check what arrived there -- without
+# drawing the rest.
+# ---------------------------------------------------------------------------------------------------------
+def normal_chunk_bf16(seed: int, index: int, shape, sigma: float = 1.0) -> np.ndarray:
+    """Chunk `index` of the tensor drawn from `seed`: N(0, sigma) as bf16 bit patterns of the given shape."""
+    return normal_bf16_bits(np.random.default_rng([int(seed), int(index)]), shape, sigma)
+
+
+ROW_CHUNK = 64          # rows per chunk of a row-chunked matrix
+COL_PANEL = 128         # columns per panel of a column-panelled matrix
+
+
+def matrix_rows_bf16(seed: int, K: int, row0: int, nrows: int, sigma: float = 1.0) -> np.ndarray:
+    """Rows [row0, row0 + nrows) of a row-chunked [M, K] matrix (chunks of ROW_CHUNK rows)."""
+    out = np.empty((nrows, K), np.uint16)
+    r = row0
+    while r < row0 + nrows:
+        c = r // ROW_CHUNK
+        chunk = normal_chunk_bf16(seed, c, (ROW_CHUNK, K), sigma)
+        lo, hi = r - c * ROW_CHUNK, min(ROW_CHUNK, row0 + nrows - c * ROW_CHUNK)
+        out[r - row0:r - row0 + hi - lo] = chunk[lo:hi]
+        r += hi - lo
+    return out
+
+
+def matrix_panels_bf16(seed: int, K: int, col0: int, ncols: int, sigma: float = 1.0) -> np.ndarray:
+    """Columns [col0, col0 + ncols) of a column-panelled [K, N] matrix (panels of COL_PANEL columns), as a
+    contiguous [K, ncols] array.  col0 and ncols are multiples of COL_PANEL."""
+    assert col0 % COL_PANEL == 0 and ncols % COL_PANEL == 0
+    out = np.empty((K, ncols), np.uint16)
+    for j in range(ncols // COL_PANEL):
+        out[:, j * COL_PANEL:(j + 1) * COL_PANEL] = normal_chunk_bf16(seed, col0 // COL_PANEL + j, (K, COL_PANEL), sigma)
+    return out
+
+
+def head_slice_bf16(seed: int, H: int, b: int, h: int, S: int, D: int, sigma: float = 1.0) -> np.ndarray:
+    """The [S, D] slice of (batch b, head h) of a [B, H, S, D] tensor chunked per (batch, head)."""
+    return normal_chunk_bf16(seed, b * H + h, (S, D), sigma)
