@@ -250,6 +250,42 @@ __device__ __forceinline__ void load_mask_chunk(const void* row_ptr, int col, in
     }
 }
 
+// Does the mask change anything in columns col0 .. col0 + 127 for the rows of this warp?  (additive: any value other
+// than +0; bool: any element clear.)  When every row reads the same values (a key-padding mask: row stride 0) the 32
+// lanes share the scan, four values each; otherwise every thread scans its own row.  Warp-uniform result.
+template <bool BOOLM>
+__device__ __forceinline__ bool mask_block_active(const char* row_ptr, bool rows_shared, int col0, int Sk, bool vec, int lane) {
+    bool any = false;
+    if (rows_shared) {
+        const int c = col0 + 4 * lane;
+        if constexpr (BOOLM) {
+            const unsigned char* m = reinterpret_cast<const unsigned char*>(row_ptr) + c;
+            if (vec && c + 4 <= Sk) any = __vcmpeq4(__ldg(reinterpret_cast<const unsigned int*>(m)), 0u) != 0u;
+            else
+                for (int i = 0; i < 4; ++i) any |= (c + i < Sk) && __ldg(m + i) == 0;
+        } else {
+            const float* m = reinterpret_cast<const float*>(row_ptr) + c;
+            if (vec && c + 4 <= Sk) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(m));
+                any = (v.x | v.y | v.z | v.w) != 0u;
+            } else {
+                for (int i = 0; i < 4; ++i) any |= (c + i < Sk) && __float_as_uint(__ldg(m + i)) != 0u;
+            }
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < BKV / 32; ++c) {
+            float add[32];
+            load_mask_chunk<BOOLM>(row_ptr, col0 + c * 32, Sk, vec, add);
+            uint32_t bits = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) bits |= __float_as_uint(add[i]);
+            any |= bits != 0u;
+        }
+    }
+    return __any_sync(0xffffffffu, any);
+}
+
 // Number of key blocks a query tile starting at row q0 needs.
 __device__ __forceinline__ int blocks_for_tile(const FaParams& p, int q0) {
     if (q0 >= p.Sq) return 0;
@@ -531,14 +567,23 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tc_fence_after();
             const int col0 = j * BKV;
             // Only the diagonal block and a ragged last block need element-wise masking.
-            const bool need_mask = !GENERAL && ((p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset) || (col0 + BKV > p.Sk));
+            // General form: does this block need its scores rewritten (a softcap, or a mask that is not all "attend"
+            // here)?  Blocks a mask leaves alone -- all of them but the boundary for a key-padding mask -- take the plain path.
+            bool rewrite = false;
+            if constexpr (GENERAL) {
+                rewrite = p.softcap > 0.0f;
+                if (!rewrite && mask_row)
+                    rewrite = p.mask_bool ? mask_block_active<true>(mask_row, p.mask_strides[2] == 0, col0, p.Sk, p.mask_vec != 0, lane)
+                                          : mask_block_active<false>(mask_row, p.mask_strides[2] == 0, col0, p.Sk, p.mask_vec != 0, lane);
+            }
+            const bool need_mask = !rewrite && ((p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset) || (col0 + BKV > p.Sk));
             const int col_limit = p.causal ? min(p.Sk - 1, qrow + p.causal_offset) : p.Sk - 1;   // last visible column of this row
-            const float sc = GENERAL ? 1.0f : p.scale_log2;     // the general form leaves log2-domain scores in tensor memory
+            const float sc = rewrite ? 1.0f : p.scale_log2;     // a rewritten block leaves log2-domain scores in tensor memory
 
             // Pass 1: the row maximum.  The 128 scores are only reduced here and die at once, so the
             // exponentiation below never competes with a whole row for registers.
             float mx;
-            if constexpr (GENERAL) {
+            if (GENERAL && rewrite) {
                 // General form: this pass also rewrites the scores in place as log2(e) * softcap(scale * s, causal rule,
                 // mask).  Order as in the reference (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added,
                 // softcap last (which turns the -inf of masked positions into -softcap); columns past Sk do not
