@@ -286,6 +286,79 @@ __device__ __forceinline__ bool mask_block_active(const char* row_ptr, bool rows
     return __any_sync(0xffffffffu, any);
 }
 
+// General form of a key block: rewrites the 128 scores of this thread's row in tensor memory as
+// log2(e) * softcap(scale * s, causal rule, mask) and returns their maximum.  Order as in the reference
+// (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added, softcap last (which turns the -inf of masked
+// positions into -softcap); columns past Sk do not exist and stay -inf.  Two halves of 64 columns, both loads of a
+// half in flight.
+__device__ __forceinline__ float rewrite_scores(const FaParams& p, uint32_t tS, const char* mask_row, int col0, int qrow, int tile_row0) {
+    const bool causal_here = p.causal && col0 + BKV - 1 > tile_row0 + p.causal_offset;
+    const bool edge = causal_here || col0 + BKV > p.Sk;
+    const int causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
+    const float cap = p.softcap, k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
+    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
+    float mx = -INFINITY;
+    auto transform = [&](uint32_t (&s)[32], const float (&add)[32], int cbase) {
+        if (cap > 0.0f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int col = cbase + i;
+                float x = __uint_as_float(s[i]) * p.scale;
+                if (edge && col > causal_limit) x = -INFINITY;
+                if (mask_row) x += add[i];
+                x = softcap_score(x, cap, k2) * LOG2E;
+                if (edge && col >= p.Sk) x = -INFINITY;
+                s[i] = __float_as_uint(x);
+            }
+        } else {
+            // no cap: log2(e) * (scale * s + mask) on packed pairs; -inf (a causal or a masked position)
+            // survives the addition either way round
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                uint64_t v = (uint64_t)s[2 * i] | ((uint64_t)s[2 * i + 1] << 32);
+                if (mask_row) {
+                    uint64_t m2 = pack_f32x2(add[2 * i], add[2 * i + 1]);
+                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m2) : "l"(m2), "l"(l2e2));
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(sc2), "l"(m2));
+                } else {
+                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(sc2));
+                }
+                s[2 * i] = (uint32_t)v;
+                s[2 * i + 1] = (uint32_t)(v >> 32);
+            }
+            if (edge) mask_chunk(s, cbase, min(causal_limit, p.Sk - 1));
+        }
+    };
+#pragma unroll 1
+    for (int half = 0; half < 2; ++half) {
+        uint32_t sa[32], sb[32];
+        tmem_ld_32x32b_x32(tS + half * 64, sa);
+        tmem_ld_32x32b_x32(tS + half * 64 + 32, sb);
+        float add[32];       // one chunk of mask values at a time (registers); the second read hits the same lines
+        auto load_add = [&](int cbase) {
+            if (!mask_row) return;
+            if (p.mask_bool) load_mask_chunk<true>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+            else load_mask_chunk<false>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+        };
+        load_add(col0 + half * 64);
+        tmem_wait_ld();
+        transform(sa, add, col0 + half * 64);
+        load_add(col0 + half * 64 + 32);
+        transform(sb, add, col0 + half * 64 + 32);
+        mx = fmaxf(mx, fmaxf(max_chunk(sa), max_chunk(sb)));
+        tmem_st_32x32b_x32(tS + half * 64, sa);
+        tmem_st_32x32b_x32(tS + half * 64 + 32, sb);
+    }
+    tmem_wait_st();
+    return mx;
+}
+
+// The same out of line, for the mask-only form: there a rewritten block is the exception (the boundary block of a
+// key-padding mask), and keeping its registers out of the caller keeps the plain path of that kernel lean.
+__device__ __noinline__ float rewrite_scores_out_of_line(const FaParams& p, uint32_t tS, const char* mask_row, int col0, int qrow, int tile_row0) {
+    return rewrite_scores(p, tS, mask_row, col0, qrow, tile_row0);
+}
+
 // Number of key blocks a query tile starting at row q0 needs.
 __device__ __forceinline__ int blocks_for_tile(const FaParams& p, int q0) {
     if (q0 >= p.Sq) return 0;
@@ -317,13 +390,16 @@ __device__ __forceinline__ WorkItem decode_item(const FaParams& p, int idx) {
     return w;
 }
 
-template <bool BF16, int HD, bool GENERAL>
+// FORM 0: plain (scale and the causal rule only); 1: with a mask (rewritten blocks out of line); 2: with a softcap
+// (every block is rewritten, inline), with or without a mask.
+template <bool BF16, int HD, int FORM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-               const FaParams p, const __grid_constant__ OStoreMaps omaps) {
+               const __grid_constant__ FaParams p, const __grid_constant__ OStoreMaps omaps) {
     constexpr int TILE_BYTES = Cfg<HD>::TILE_BYTES, HALF_BYTES = Cfg<HD>::HALF_BYTES, KV_STAGES = Cfg<HD>::KV_STAGES;
     constexpr int SMEM_Q = Cfg<HD>::SMEM_Q, SMEM_K = Cfg<HD>::SMEM_K, SMEM_V = Cfg<HD>::SMEM_V, NUM_BARS = Cfg<HD>::NUM_BARS;
     constexpr int NH = HD / 64;      // 64-column boxes per tile
+    constexpr bool GENERAL = FORM != 0;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sQ = smem_u32(smem), sK = sQ + SMEM_Q, sV = sK + SMEM_K;
@@ -558,6 +634,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mask_row = (const char*)p.mask + ((int64_t)batch * p.mask_strides[0] + (int64_t)head * p.mask_strides[1] +
                                                   (int64_t)min(qrow, p.Sq - 1) * p.mask_strides[2]) * (p.mask_bool ? 1 : 4);
         }
+        // A mask whose rows are all the same (a key-padding mask): the 32 lanes share the scan "does it change anything
+        // in this block", four values each, fetched one block ahead.  A block that is not whole counts as changed.
+        const bool mask_shared = GENERAL && mask_row != nullptr && p.mask_strides[2] == 0 && p.mask_vec != 0 && p.softcap <= 0.0f;
+        auto scan_fetch = [&](int jb) {
+            const int c = jb * BKV + 4 * lane;
+            if (c + 4 > p.Sk) return p.mask_bool ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(1u, 0u, 0u, 0u);
+            if (p.mask_bool) return make_uint4(__ldg(reinterpret_cast<const unsigned int*>(mask_row + c)), 0u, 0u, 0u);
+            return __ldg(reinterpret_cast<const uint4*>(mask_row + 4 * c));
+        };
+        uint4 scan_next = make_uint4(0u, 0u, 0u, 0u);
+        if (mask_shared && nblk > 0) scan_next = scan_fetch(0);
         float m_used = -INFINITY;   // maximum the stored P and O are expressed against (log2 domain)
         float l = 0.0f;
         for (int j = 0; j < nblk && ok; ++j) {
@@ -572,9 +659,16 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             bool rewrite = false;
             if constexpr (GENERAL) {
                 rewrite = p.softcap > 0.0f;
-                if (!rewrite && mask_row)
+                if (!rewrite && mask_shared) {
+                    // the lanes' four values each of this block were requested one block ago; request the next block's now
+                    const uint4 cur = scan_next;
+                    if (j + 1 < nblk) scan_next = scan_fetch(j + 1);
+                    const bool any = p.mask_bool ? __vcmpeq4(cur.x, 0u) != 0u : (cur.x | cur.y | cur.z | cur.w) != 0u;
+                    rewrite = __any_sync(0xffffffffu, any);
+                } else if (!rewrite && mask_row) {
                     rewrite = p.mask_bool ? mask_block_active<true>(mask_row, p.mask_strides[2] == 0, col0, p.Sk, p.mask_vec != 0, lane)
                                           : mask_block_active<false>(mask_row, p.mask_strides[2] == 0, col0, p.Sk, p.mask_vec != 0, lane);
+                }
             }
             const bool need_mask = !rewrite && ((p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset) || (col0 + BKV > p.Sk));
             const int col_limit = p.causal ? min(p.Sk - 1, qrow + p.causal_offset) : p.Sk - 1;   // last visible column of this row
@@ -584,68 +678,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // exponentiation below never competes with a whole row for registers.
             float mx;
             if (GENERAL && rewrite) {
-                // General form: this pass also rewrites the scores in place as log2(e) * softcap(scale * s, causal rule,
-                // mask).  Order as in the reference (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added,
-                // softcap last (which turns the -inf of masked positions into -softcap); columns past Sk do not
-                // exist and stay -inf.  Two halves of 64 columns, both loads and the mask reads of a half in flight.
-                const bool causal_here = p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset;
-                const bool edge = causal_here || col0 + BKV > p.Sk;
-                const int causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
-                const float cap = p.softcap, k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
-                const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
-                mx = -INFINITY;
-                auto transform = [&](uint32_t (&s)[32], const float (&add)[32], int cbase) {
-                    if (cap > 0.0f) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int col = cbase + i;
-                            float x = __uint_as_float(s[i]) * p.scale;
-                            if (edge && col > causal_limit) x = -INFINITY;
-                            if (mask_row) x += add[i];
-                            x = softcap_score(x, cap, k2) * LOG2E;
-                            if (edge && col >= p.Sk) x = -INFINITY;
-                            s[i] = __float_as_uint(x);
-                        }
-                    } else {
-                        // no cap: log2(e) * (scale * s + mask) on packed pairs; -inf (a causal or a masked position)
-                        // survives the addition either way round
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            uint64_t v = (uint64_t)s[2 * i] | ((uint64_t)s[2 * i + 1] << 32);
-                            if (mask_row) {
-                                uint64_t m2 = pack_f32x2(add[2 * i], add[2 * i + 1]);
-                                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m2) : "l"(m2), "l"(l2e2));
-                                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(sc2), "l"(m2));
-                            } else {
-                                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(sc2));
-                            }
-                            s[2 * i] = (uint32_t)v;
-                            s[2 * i + 1] = (uint32_t)(v >> 32);
-                        }
-                        if (edge) mask_chunk(s, cbase, min(causal_limit, p.Sk - 1));
-                    }
-                };
-#pragma unroll 1
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t sa[32], sb[32];
-                    tmem_ld_32x32b_x32(tS + half * 64, sa);
-                    tmem_ld_32x32b_x32(tS + half * 64 + 32, sb);
-                    float add[32];       // one chunk of mask values at a time (registers); the second read hits the same lines
-                    auto load_add = [&](int cbase) {
-                        if (!mask_row) return;
-                        if (p.mask_bool) load_mask_chunk<true>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
-                        else load_mask_chunk<false>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
-                    };
-                    load_add(col0 + half * 64);
-                    tmem_wait_ld();
-                    transform(sa, add, col0 + half * 64);
-                    load_add(col0 + half * 64 + 32);
-                    transform(sb, add, col0 + half * 64 + 32);
-                    mx = fmaxf(mx, fmaxf(max_chunk(sa), max_chunk(sb)));
-                    tmem_st_32x32b_x32(tS + half * 64, sa);
-                    tmem_st_32x32b_x32(tS + half * 64 + 32, sb);
-                }
-                tmem_wait_st();
+                // rare for a key-padding mask (its boundary blocks only), every block under a softcap: kept out of line so
+                // that the plain path keeps its registers
+                if constexpr (FORM == 2) mx = rewrite_scores(p, tS, mask_row, col0, qrow, q0 + t * BQ);
+                else mx = rewrite_scores_out_of_line(p, tS, mask_row, col0, qrow, q0 + t * BQ);
             } else {
                 uint32_t s0[32], s1[32], s2[32], s3[32];
                 tmem_ld_32x32b_x32(tS, s0);
@@ -929,7 +965,8 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
         p.mask_vec = d.mask && (reinterpret_cast<uintptr_t>(d.mask) & 15) == 0 && p.mask_strides[0] % per16 == 0 &&
                      p.mask_strides[1] % per16 == 0 && p.mask_strides[2] % per16 == 0;
     }
-    const bool general = d.mask != nullptr || p.softcap > 0.0f;
+    const int form = p.softcap > 0.0f ? 2 : (d.mask != nullptr ? 1 : 0);
+    const bool general = form != 0;
     p.O = d.O;
     p.lse = d.lse;
     for (int i = 0; i < 3; ++i) p.o_strides[i] = d.o_strides[i];
@@ -965,14 +1002,19 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     };
     const bool bf = d.dtype == MK_BF16;
     const int smem128 = p.tma_o ? Cfg<128>::SMEM_BYTES_DELIVER : Cfg<128>::SMEM_BYTES, smem64 = p.tma_o ? Cfg<64>::SMEM_BYTES_DELIVER : Cfg<64>::SMEM_BYTES;
-#define MK_FA(BF, HD_, GEN, SMEM) MK_CUDA(launch(sdpa_tc_kernel<BF, HD_, GEN>, SMEM))
+#define MK_FA(BF, HD_, FORM_, SMEM) MK_CUDA(launch(sdpa_tc_kernel<BF, HD_, FORM_>, SMEM))
+#define MK_FA_FORMS(BF, HD_, SMEM)                          \
+    do {                                                    \
+        if (form == 2) MK_FA(BF, HD_, 2, SMEM);             \
+        else if (form == 1) MK_FA(BF, HD_, 1, SMEM);        \
+        else MK_FA(BF, HD_, 0, SMEM);                       \
+    } while (0)
     if (HDk == 128) {
-        if (general) { if (bf) MK_FA(true, 128, true, smem128); else MK_FA(false, 128, true, smem128); }
-        else { if (bf) MK_FA(true, 128, false, smem128); else MK_FA(false, 128, false, smem128); }
+        if (bf) MK_FA_FORMS(true, 128, smem128); else MK_FA_FORMS(false, 128, smem128);
     } else {
-        if (general) { if (bf) MK_FA(true, 64, true, smem64); else MK_FA(false, 64, true, smem64); }
-        else { if (bf) MK_FA(true, 64, false, smem64); else MK_FA(false, 64, false, smem64); }
+        if (bf) MK_FA_FORMS(true, 64, smem64); else MK_FA_FORMS(false, 64, smem64);
     }
+#undef MK_FA_FORMS
 #undef MK_FA
     MK_CUDA(cudaGetLastError());
     note_launch(dev, st, HDk == 128 ? (general ? "sdpa_tc_d128_general" : "sdpa_tc_d128") : (general ? "sdpa_tc_d64_general" : "sdpa_tc_d64"));
