@@ -50,6 +50,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 
+// Non-blocking probe: has the phase with this parity completed?  (try_wait may suspend the thread for a while; this never does.)
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+
 // Bounded wait.  Returns true when the phase completed.  Gives up when (a) another thread of the
 // CTA already raised *abort_flag, or (b) ~kWaitLimitNs elapse; in case (b) it raises the flag and
 // records `code` in the device error word.  Callers leave their loops on false; nothing traps

@@ -51,7 +51,7 @@ struct Cfg {
     static constexpr int SMEM_Q = 2 * TILE_BYTES;
     static constexpr int SMEM_K = KV_STAGES * TILE_BYTES;
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 2;
+    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 2 + 2;
     static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + 1024 + 512;      // + alignment slack + barriers and slots
     // head-sharded runs that deliver O by tile stores stage one 128-row tile of output beside the operands
     static constexpr int SMEM_BYTES_DELIVER = SMEM_BYTES + TILE_BYTES;
@@ -61,7 +61,15 @@ struct Cfg {
 struct OStoreMaps {
     CUtensorMap m[1 + MK_MAX_PEERS];
 };
-constexpr int NUM_THREADS = 352;        // 11 warps
+constexpr int NUM_THREADS = 384;        // 12 warps = 3 warpgroups (register rebalancing works per warpgroup); warp 11 idles
+// 384 threads start with 168 registers each.  The control warpgroup keeps 56, which frees 128 * 112 = 14336 registers;
+// the two softmax warpgroups take 224 each: 2 * 128 * 56 = 14336.
+constexpr int REGS_LAUNCH = 168, REGS_CONTROL = 56, REGS_SOFTMAX = 224;
+static_assert(2 * 128 * (REGS_SOFTMAX - REGS_LAUNCH) <= 128 * (REGS_LAUNCH - REGS_CONTROL), "register budget of the rebalancing");
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr int TMEM_COLS = 512;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 domain: P stays below 2^8
@@ -155,8 +163,7 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], float scale_l
 // f in [-0.5, 0.5]; 2^f by minimax polynomial, relative error 7.5e-5, far below the 16-bit rounding of P;
 // 2^n by adding n to the exponent field) balances the two pipes: 1738 instead of 2083 clocks for two
 // warps in isolation.
-constexpr int POLY_EVERY = 4;
-template <bool BF16>
+template <bool BF16, int POLY_EVERY>
 __device__ __forceinline__ void exp_chunk_mixed(const uint32_t (&s)[32], float scale_log2, float neg_m, uint64_t& sum2, uint32_t* pk) {
     const uint64_t sc2 = pack_f32x2(scale_log2, scale_log2), nm2 = pack_f32x2(neg_m, neg_m);
     const uint64_t magic2 = pack_f32x2(12582912.0f, 12582912.0f);
@@ -400,6 +407,10 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     constexpr int SMEM_Q = Cfg<HD>::SMEM_Q, SMEM_K = Cfg<HD>::SMEM_K, SMEM_V = Cfg<HD>::SMEM_V, NUM_BARS = Cfg<HD>::NUM_BARS;
     constexpr int NH = HD / 64;      // 64-column boxes per tile
     constexpr bool GENERAL = FORM != 0;
+    // P is published in two halves of 64 keys, so that the first four P V steps run while the second half is exponentiated.
+    // 64-wide heads are bound by the softmax warps, not by the chain softmax -> P V -> next S: there the second barrier only costs.
+    constexpr bool P_HALVES = HD == 128;
+    constexpr int PE = HD == 128 ? 4 : 3;     // every PE-th pair of exponentials runs on the FMA pipes (measured best per head size)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sQ = smem_u32(smem), sK = sQ + SMEM_Q, sV = sK + SMEM_K;
@@ -421,6 +432,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bar_iempty = bar_ifull + 16;              // [2] work-item slot read by every consumer
     const uint32_t bar_ostage_full = bar_iempty + 16;        // output staging tile written by the four warps of a query tile
     const uint32_t bar_ostage_free = bar_ostage_full + 8;    // ... and read out by the tile stores warp 10 issued
+    const uint32_t bar_phalf = bar_ostage_free + 8;          // [2] first 64 keys of P_t written (only when P is published in halves)
     volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2] claimed item indices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -440,6 +452,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_sfull + 8 * t, 1);
             mbar_init(bar_pfull + 8 * t, 128);
+            mbar_init(bar_phalf + 8 * t, 128);
             mbar_init(bar_pvdone + 8 * t, 1);
             mbar_init(bar_ofree + 8 * t, 4);   // one lane per softmax warp of the tile
             mbar_init(bar_ifull + 8 * t, 1);
@@ -468,7 +481,12 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     // of a head first, so the CTAs running at any moment share few heads (K/V stay in L2), the
     // cheapest items come last (short tail), and the epilogue of one item overlaps the loads and
     // first MMAs of the next.  The producer publishes each claimed index through a two-slot ring.
-    if (warp == 8) {
+    // Registers are rebalanced between the warpgroups first: warps 8-11 (producer, MMA issuer, allocation / stores, one
+    // idle warp) keep REGS_CONTROL each, and the two softmax warpgroups take REGS_SOFTMAX -- every warp of a warpgroup
+    // executes the same instruction, before anything that could make another warp wait.
+    if (warp >= 8) {
+      setmaxnreg_dec<REGS_CONTROL>();
+      if (warp == 8) {
         // ---------------------------------------------------------------- TMA producer + item claims
         // Warp-uniform like the MMA issuer: all lanes run the loops and waits, lane 0 claims and copies.
         {
@@ -519,7 +537,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
         }
-    } else if (warp == 9) {
+      } else if (warp == 9) {
         // ---------------------------------------------------------------- MMA issuer
         // All 32 lanes run the loops and the waits so that descriptors and addresses stay warp-uniform;
         // one elected lane issues the tensor-core instructions.
@@ -537,14 +555,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
                 mma_commit_lead(bar_sfull + 8 * t, leader);
             };
-            auto issue_pv = [&](int t, int vstage, bool accumulate) {
+            auto issue_pv_steps = [&](int t, int vstage, bool accumulate, int ks0, int ks1) {
                 const uint64_t vd = desc_v + (uint32_t)((vstage * TILE_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < BKV / 16; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     mma_f16_ts_lead(tm + 256 + t * 128, tm + t * 128 + ks * 8, vd + (uint32_t)((ks * (16 * 128)) >> 4), p.idesc_pv,
                                     (accumulate || ks != 0) ? 1u : 0u, leader);
                 }
-                mma_commit_lead(bar_pvdone + 8 * t, leader);
             };
             int stage = 0;            // K/V ring position, carried across work items
             uint32_t phase = 0;
@@ -578,10 +595,17 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                             ok = __all_sync(0xffffffffu, mbar_wait(bar_ofree + 8 * t, (used[t] & 1) ^ 1, abort_flag, p.kerr, KERR_SDPA_MMA_WAIT, 700000 + n));
                             if (!ok) break;
                         }
+                        if constexpr (P_HALVES) {
+                            ok = __all_sync(0xffffffffu, mbar_wait(bar_phalf + 8 * t, (cum[t] + j) & 1, abort_flag, p.kerr, KERR_SDPA_MMA_WAIT, 350000 + j));
+                            if (!ok) break;
+                            tc_fence_after();
+                            issue_pv_steps(t, stage, j > 0, 0, BKV / 32);
+                        }
                         ok = __all_sync(0xffffffffu, mbar_wait(bar_pfull + 8 * t, (cum[t] + j) & 1, abort_flag, p.kerr, KERR_SDPA_MMA_WAIT, 300000 + j));
                         if (!ok) break;
                         tc_fence_after();
-                        issue_pv(t, stage, j > 0);
+                        issue_pv_steps(t, stage, j > 0, P_HALVES ? BKV / 32 : 0, BKV / 16);
+                        mma_commit_lead(bar_pvdone + 8 * t, leader);
                         if (j + 1 < w.nblk[t]) {
                             if (!k_next_ready) {
                                 ok = __all_sync(0xffffffffu, mbar_wait(bar_kfull + 8 * nstage, nphase, abort_flag, p.kerr, KERR_SDPA_MMA_WAIT, 400000 + j));
@@ -605,7 +629,44 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 }
             }
         }
-    } else if (warp < 8) {
+      } else if (warp == 10 && p.tma_o) {
+        // ---------------------------------------------------------------- tile stores of finished output tiles
+        // Follows the work items like every other consumer; for each query tile that had work it waits until the four
+        // softmax warps have staged the tile, issues one tile store per 64-column box and destination (the local O and
+        // every peer's O over NVLink), and frees the staging tile once the copy engine has read it.
+        uint32_t u = 0;
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+            const int slot = n & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar_ifull + 8 * slot, (n >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 500000 + n));
+            if (!ok) break;
+            const int idx = __reduce_max_sync(0xffffffffu, (int)item_slot[slot]);
+            if (lane == 0) mbar_arrive(bar_iempty + 8 * slot);
+            if (idx >= total_items) break;
+            const WorkItem w = decode_item(p, idx);
+            for (int t = 0; t < 2 && ok; ++t) {
+                if (w.nblk[t] == 0) continue;
+                ok = __all_sync(0xffffffffu, mbar_wait(bar_ostage_full, u & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, n));
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t src = smem_u32(stageO);
+#pragma unroll
+                    for (int h = 0; h < NH; ++h)
+                        for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * HALF_BYTES, h * 64, w.q0 + t * BQ, w.head, w.batch);
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();
+                    mbar_arrive(bar_ostage_free);
+                }
+                __syncwarp();
+                ++u;
+            }
+        }
+        if (lane == 0) bulk_wait_group<0>();     // every tile store has completed before the CTA may leave
+        __syncwarp();
+    
+      }
+    } else {
+        setmaxnreg_inc<REGS_SOFTMAX>();
         // ---------------------------------------------------------------- softmax / correction / epilogue
         const int t = warp >> 2;                 // query tile
         const int quarter = warp & 3;            // tensor-memory lane quarter of this warp
@@ -674,34 +735,28 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             const int col_limit = p.causal ? min(p.Sk - 1, qrow + p.causal_offset) : p.Sk - 1;   // last visible column of this row
             const float sc = rewrite ? 1.0f : p.scale_log2;     // a rewritten block leaves log2-domain scores in tensor memory
 
-            // Pass 1: the row maximum.  The 128 scores are only reduced here and die at once, so the
-            // exponentiation below never competes with a whole row for registers.
-            float mx;
+            // One pass over the row: with the registers the rebalancing gives the softmax warps, all 128 scores stay in
+            // registers from the row maximum through the exponentials -- no second read of S from tensor memory.
+            float mx_rewritten = 0.0f;
             if (GENERAL && rewrite) {
-                // rare for a key-padding mask (its boundary blocks only), every block under a softcap: kept out of line so
-                // that the plain path keeps its registers
-                if constexpr (FORM == 2) mx = rewrite_scores(p, tS, mask_row, col0, qrow, q0 + t * BQ);
-                else mx = rewrite_scores_out_of_line(p, tS, mask_row, col0, qrow, q0 + t * BQ);
-            } else {
-                uint32_t s0[32], s1[32], s2[32], s3[32];
-                tmem_ld_32x32b_x32(tS, s0);
-                tmem_ld_32x32b_x32(tS + 32, s1);
-                tmem_ld_32x32b_x32(tS + 64, s2);
-                tmem_ld_32x32b_x32(tS + 96, s3);
-                tmem_wait_ld();
-                if (need_mask) {   // masked scores become -inf: they drop out of the max and exponentiate to 0
-                    mask_chunk(s0, col0, col_limit);
-                    mask_chunk(s1, col0 + 32, col_limit);
-                    mask_chunk(s2, col0 + 64, col_limit);
-                    mask_chunk(s3, col0 + 96, col_limit);
-                }
-                mx = fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
+                // rare for a key-padding mask (its boundary blocks only), every block under a softcap
+                if constexpr (FORM == 2) mx_rewritten = rewrite_scores(p, tS, mask_row, col0, qrow, q0 + t * BQ);
+                else mx_rewritten = rewrite_scores_out_of_line(p, tS, mask_row, col0, qrow, q0 + t * BQ);
             }
-            // Pass 2 reads the row again, 32 columns at a time; the first two chunks are requested now
-            // so that their latency hides behind the bookkeeping below.
-            uint32_t ca[32], cb[32];
-            tmem_ld_32x32b_x32(tS, ca);
-            tmem_ld_32x32b_x32(tS + 32, cb);
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_ld_32x32b_x32(tS, s0);
+            tmem_ld_32x32b_x32(tS + 32, s1);
+            tmem_ld_32x32b_x32(tS + 64, s2);
+            tmem_ld_32x32b_x32(tS + 96, s3);
+            tmem_wait_ld();
+            if (need_mask) {   // masked scores become -inf: they drop out of the max and exponentiate to 0
+                mask_chunk(s0, col0, col_limit);
+                mask_chunk(s1, col0 + 32, col_limit);
+                mask_chunk(s2, col0 + 64, col_limit);
+                mask_chunk(s3, col0 + 96, col_limit);
+            }
+            const float mx = (GENERAL && rewrite) ? mx_rewritten
+                                                  : fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
             const float m_new = fmaxf(m_used, mx * sc);
             float alpha = 1.0f;
             bool need = false;
@@ -714,10 +769,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // O_t is only touched between "P V of block j-1 retired" and "P of block j published".
                 ok = mbar_wait(bar_pvdone + 8 * t, (cum + j - 1) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 100000 + j);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) {
-                    tmem_wait_ld();   // no load may be in flight when the warp leaves
-                    break;
-                }
+                if (!ok) break;
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
@@ -731,31 +783,21 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             l *= alpha;
 
-            // P = exp2(S * scale_log2 - m) on packed f32 pairs, rounded to 16 bit, written over S.  P of
-            // chunk c lands on columns [16c, 16c+16), which the reads of chunks <= c/2 have left behind.
+            // P = exp2(S * scale_log2 - m) on packed f32 pairs, rounded to 16 bit, written over S (every score has
+            // been read by now, so P can land anywhere in the S columns).
             const float neg_m = (m_used == -INFINITY) ? 0.0f : -m_used;   // a fully masked row keeps P = 0
             uint64_t sum2 = 0;                                            // two partial row sums (f32x2)
             uint32_t pk[32];
-            tmem_wait_ld();
-            pin_regs(ca);
-            pin_regs(cb);
-            if (need_mask) {
-                mask_chunk(ca, col0, col_limit);
-                mask_chunk(cb, col0 + 32, col_limit);
-            }
-            exp_chunk_mixed<BF16>(ca, sc, neg_m, sum2, pk);
-            tmem_ld_32x32b_x32(tS + 64, ca);
-            exp_chunk_mixed<BF16>(cb, sc, neg_m, sum2, pk + 16);
-            tmem_wait_ld();
-            pin_regs(ca);
-            tmem_ld_32x32b_x32(tS + 96, cb);
+            exp_chunk_mixed<BF16, PE>(s0, sc, neg_m, sum2, pk);
+            exp_chunk_mixed<BF16, PE>(s1, sc, neg_m, sum2, pk + 16);
             tmem_st_32x32b_x32(tS, pk);
-            if (need_mask) mask_chunk(ca, col0 + 64, col_limit);
-            exp_chunk_mixed<BF16>(ca, sc, neg_m, sum2, pk);
-            tmem_wait_ld();
-            pin_regs(cb);
-            if (need_mask) mask_chunk(cb, col0 + 96, col_limit);
-            exp_chunk_mixed<BF16>(cb, sc, neg_m, sum2, pk + 16);
+            exp_chunk_mixed<BF16, PE>(s2, sc, neg_m, sum2, pk);
+            if constexpr (P_HALVES) {
+                tmem_wait_st();                  // the first store has long landed: publish the first 64 keys of P
+                tc_fence_before();
+                mbar_arrive(bar_phalf + 8 * t);
+            }
+            exp_chunk_mixed<BF16, PE>(s3, sc, neg_m, sum2, pk + 16);
             tmem_st_32x32b_x32(tS + 32, pk);
             l += lo_f32(sum2) + hi_f32(sum2);
             tmem_wait_st();
@@ -845,42 +887,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         stage_uses += (w.nblk[0] > 0 ? 1u : 0u) + (w.nblk[1] > 0 ? 1u : 0u);
         cum += nblk;
       }
-    }
-
-    else if (warp == 10 && p.tma_o) {
-        // ---------------------------------------------------------------- tile stores of finished output tiles
-        // Follows the work items like every other consumer; for each query tile that had work it waits until the four
-        // softmax warps have staged the tile, issues one tile store per 64-column box and destination (the local O and
-        // every peer's O over NVLink), and frees the staging tile once the copy engine has read it.
-        uint32_t u = 0;
-        bool ok = true;
-        for (int n = 0; ok; ++n) {
-            const int slot = n & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar_ifull + 8 * slot, (n >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, 500000 + n));
-            if (!ok) break;
-            const int idx = __reduce_max_sync(0xffffffffu, (int)item_slot[slot]);
-            if (lane == 0) mbar_arrive(bar_iempty + 8 * slot);
-            if (idx >= total_items) break;
-            const WorkItem w = decode_item(p, idx);
-            for (int t = 0; t < 2 && ok; ++t) {
-                if (w.nblk[t] == 0) continue;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar_ostage_full, u & 1, abort_flag, p.kerr, KERR_SDPA_STORE_WAIT, n));
-                if (!ok) break;
-                if (lane == 0) {
-                    const uint32_t src = smem_u32(stageO);
-#pragma unroll
-                    for (int h = 0; h < NH; ++h)
-                        for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * HALF_BYTES, h * 64, w.q0 + t * BQ, w.head, w.batch);
-                    bulk_commit_group();
-                    bulk_wait_group_read<0>();
-                    mbar_arrive(bar_ostage_free);
-                }
-                __syncwarp();
-                ++u;
-            }
-        }
-        if (lane == 0) bulk_wait_group<0>();     // every tile store has completed before the CTA may leave
-        __syncwarp();
     }
 
     if (*abort_flag) __nanosleep(2000000);
@@ -997,6 +1003,12 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     auto launch = [&](auto kernel, int smem_bytes) -> cudaError_t {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
         if (e != cudaSuccess) return e;
+        // the register increase of the softmax warpgroups is only satisfiable if the kernel starts with REGS_LAUNCH
+        // registers per thread: checked here, never assumed
+        cudaFuncAttributes fa{};
+        e = cudaFuncGetAttributes(&fa, kernel);
+        if (e != cudaSuccess) return e;
+        if (fa.numRegs < REGS_LAUNCH) return cudaErrorLaunchOutOfResources;
         kernel<<<(unsigned)grid, NUM_THREADS, smem_bytes, st>>>(tq, tk, tv, p, omaps);
         return cudaSuccess;
     };

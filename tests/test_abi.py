@@ -29,6 +29,16 @@ def test_header_symbols_exported_and_bound():
     assert lib.mk_abi_version() == 4
 
 
+def test_rust_shim_declares_every_header_symbol():
+    """ffi/morok_b200_device.rs (uncompiled: no Rust toolchain here) stays in step with the header."""
+    text = open(os.path.join(ROOT, "ffi", "morok_b200_device.rs")).read()
+    declared = set(re.findall(r"pub fn (mk_\w+)\(", text))
+    assert declared == set(declared_symbols()), (set(declared_symbols()) - declared, declared - set(declared_symbols()))
+    # the struct mirrors carry the fields the header added last
+    for field in ("mask_kind", "mask_strides", "causal_offset", "b2", "d2"):
+        assert f"pub {field}:" in text
+
+
 def test_struct_layouts_match_header():
     lib = _ffi.load()
     # the natural-alignment sizes of the declared field lists ...
