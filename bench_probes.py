@@ -5,7 +5,7 @@ commands the summaries under profiles/ were made with.
 
     gemm [M K N] [--f16] [--nt]        bf16 tensor-core GEMM (default 4096 4096 8192; inputs exceed L2)
     attn [B H S D] [--noncausal]       causal attention forward (default 2 16 4096 128)
-    attn_mask [B H S D] [--softcap X]  the same with a per-batch padding mask (and a softcap)
+    attn_mask [B H S D] [--softcap X] [--zero-mask]  the same with a per-batch padding mask (and a softcap)
     skinny [rows N K]                  few-row GEMM against `linear` weights [N, K]
     decode [batch kv_len]              decode attention: one query row per sequence against a long cache
     layer [batch seq hidden q_heads kv_heads ffn] [--plan]     one decoder layer through the Tensor API
@@ -23,7 +23,8 @@ from morok_b200 import Tensor, synth
 
 
 def _ints(args, n, default):
-    vals = [int(a) for a in args if not a.startswith("--")]
+    skip = {i + 1 for i, a in enumerate(args) if a == "--softcap"}      # the value of an option is not a dimension
+    vals = [int(a) for i, a in enumerate(args) if not a.startswith("--") and i not in skip]
     return tuple(vals) if len(vals) == n else default
 
 
@@ -65,8 +66,9 @@ def attn(args, masked=False):
     kw = {}
     if masked:       # a padding mask per batch element: the last keys of each sequence are hidden
         m = np.zeros((B, 1, 1, S), np.float32)
-        for b in range(B):
-            m[b, :, :, S - 64 * (b + 1):] = -np.inf
+        if "--zero-mask" not in args:      # (--zero-mask: a mask that changes nothing -- the cost of asking)
+            for b in range(B):
+                m[b, :, :, S - 64 * (b + 1):] = -np.inf
         kw = dict(mask=dev.from_numpy(m), mask_strides=(S, 0, 0))
     ms = _timed(dev, lambda: dev.sdpa(q, k, v, o, B, H, H, S, S, D, dtype=mk.MK_BF16, causal=causal, softcap=softcap, **kw))
     flops = (2.0 if causal else 4.0) * B * H * S * S * D

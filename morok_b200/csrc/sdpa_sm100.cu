@@ -31,6 +31,7 @@
 // kernel: its general form rewrites the scores in tensor memory during the row-maximum pass.
 // All barrier waits are bounded; a wait that gives up records a code in the device error word.
 #include <cstdlib>
+#include <type_traits>
 
 #include "ptx_sm100.cuh"
 
@@ -217,12 +218,6 @@ __device__ __forceinline__ float fast_rcp(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// cap * tanh(x / cap) with tanh(z) = 1 - 2 / (1 + e^(2z)): -inf gives -cap, as the reference's tanh after masking does.
-__device__ __forceinline__ float softcap_score(float x, float cap, float two_log2e_over_cap) {
-    const float e = poly_exp2(x * two_log2e_over_cap);
-    return cap * fmaf(-2.0f, fast_rcp(1.0f + e), 1.0f);
-}
-
 // 32 consecutive mask values of one row as additive terms (bool: 0 where set, -inf where clear); columns >= Sk read as 0.
 template <bool BOOLM>
 __device__ __forceinline__ void load_mask_chunk(const void* row_ptr, int col, int Sk, bool vec, float (&add)[32]) {
@@ -293,77 +288,70 @@ __device__ __forceinline__ bool mask_block_active(const char* row_ptr, bool rows
     return __any_sync(0xffffffffu, any);
 }
 
-// General form of a key block: rewrites the 128 scores of this thread's row in tensor memory as
-// log2(e) * softcap(scale * s, causal rule, mask) and returns their maximum.  Order as in the reference
-// (tensor/src/transformer.rs:98-132): scale, causal -inf, mask added, softcap last (which turns the -inf of masked
-// positions into -softcap); columns past Sk do not exist and stay -inf.  Two halves of 64 columns, both loads of a
-// half in flight.
-__device__ __forceinline__ float rewrite_scores(const FaParams& p, uint32_t tS, const char* mask_row, int col0, int qrow, int tile_row0) {
+// General form of a key block: rewrites 32 scores of this thread's row, held in registers, as
+// log2(e) * softcap(scale * s, causal rule, mask).  Order as in the reference (tensor/src/transformer.rs:98-132):
+// scale, causal -inf, mask added, softcap last (which turns the -inf of masked positions into -softcap); columns
+// past Sk do not exist and stay -inf.  `add` holds the chunk's 32 mask values when there is a mask.
+struct RewriteConsts {
+    bool edge, has_mask;
+    int causal_limit;
+    float cap, k2;
+};
+__device__ __forceinline__ RewriteConsts rewrite_consts(const FaParams& p, const char* mask_row, int col0, int qrow, int tile_row0) {
+    RewriteConsts c;
     const bool causal_here = p.causal && col0 + BKV - 1 > tile_row0 + p.causal_offset;
-    const bool edge = causal_here || col0 + BKV > p.Sk;
-    const int causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
-    const float cap = p.softcap, k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
-    const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
-    float mx = -INFINITY;
-    auto transform = [&](uint32_t (&s)[32], const float (&add)[32], int cbase) {
-        if (cap > 0.0f) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int col = cbase + i;
-                float x = __uint_as_float(s[i]) * p.scale;
-                if (edge && col > causal_limit) x = -INFINITY;
-                if (mask_row) x += add[i];
-                x = softcap_score(x, cap, k2) * LOG2E;
-                if (edge && col >= p.Sk) x = -INFINITY;
-                s[i] = __float_as_uint(x);
-            }
-        } else {
-            // no cap: log2(e) * (scale * s + mask) on packed pairs; -inf (a causal or a masked position)
-            // survives the addition either way round
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                uint64_t v = (uint64_t)s[2 * i] | ((uint64_t)s[2 * i + 1] << 32);
-                if (mask_row) {
-                    uint64_t m2 = pack_f32x2(add[2 * i], add[2 * i + 1]);
-                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m2) : "l"(m2), "l"(l2e2));
-                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(sc2), "l"(m2));
-                } else {
-                    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(sc2));
-                }
-                s[2 * i] = (uint32_t)v;
-                s[2 * i + 1] = (uint32_t)(v >> 32);
-            }
-            if (edge) mask_chunk(s, cbase, min(causal_limit, p.Sk - 1));
-        }
-    };
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-        uint32_t sa[32], sb[32];
-        tmem_ld_32x32b_x32(tS + half * 64, sa);
-        tmem_ld_32x32b_x32(tS + half * 64 + 32, sb);
-        float add[32];       // one chunk of mask values at a time (registers); the second read hits the same lines
-        auto load_add = [&](int cbase) {
-            if (!mask_row) return;
-            if (p.mask_bool) load_mask_chunk<true>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
-            else load_mask_chunk<false>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
-        };
-        load_add(col0 + half * 64);
-        tmem_wait_ld();
-        transform(sa, add, col0 + half * 64);
-        load_add(col0 + half * 64 + 32);
-        transform(sb, add, col0 + half * 64 + 32);
-        mx = fmaxf(mx, fmaxf(max_chunk(sa), max_chunk(sb)));
-        tmem_st_32x32b_x32(tS + half * 64, sa);
-        tmem_st_32x32b_x32(tS + half * 64 + 32, sb);
-    }
-    tmem_wait_st();
-    return mx;
+    c.edge = causal_here || col0 + BKV > p.Sk;
+    c.has_mask = mask_row != nullptr;
+    c.causal_limit = p.causal ? qrow + p.causal_offset : 0x7fffffff;
+    c.cap = p.softcap;
+    c.k2 = p.softcap > 0.0f ? 2.0f * LOG2E / p.softcap : 0.0f;
+    return c;
 }
-
-// The same out of line, for the mask-only form: there a rewritten block is the exception (the boundary block of a
-// key-padding mask), and keeping its registers out of the caller keeps the plain path of that kernel lean.
-__device__ __noinline__ float rewrite_scores_out_of_line(const FaParams& p, uint32_t tS, const char* mask_row, int col0, int qrow, int tile_row0) {
-    return rewrite_scores(p, tS, mask_row, col0, qrow, tile_row0);
+__device__ __forceinline__ void load_mask_values(const FaParams& p, const char* mask_row, int cbase, float (&add)[32]) {
+    if (!mask_row) return;
+    if (p.mask_bool) load_mask_chunk<true>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+    else load_mask_chunk<false>(mask_row, cbase, p.Sk, p.mask_vec != 0, add);
+}
+template <bool CAP>
+__device__ __forceinline__ void rewrite_chunk(const FaParams& p, const RewriteConsts& c, uint32_t (&s)[32], const float (&add)[32], int cbase) {
+    if constexpr (CAP) {
+        // log2(e) * cap * tanh(x / cap) with tanh(z) = 1 - 2 / (1 + 2^(z * 2 log2 e)): the power of two alternately on the
+        // special-function unit and on the FMA pipes, like the exponentials of P; one rcp.approx per score; -inf (a masked
+        // position) gives -cap as in the reference.  Plain f32 instructions: the packed f32x2 form of this chain measured
+        // 40 % slower (the clamp, the exponent arithmetic and the reciprocal have no packed form; the pairs are taken apart
+        // and put together again around them).
+        const float cap_l2 = c.cap * LOG2E;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const int col = cbase + i;
+            float x = __uint_as_float(s[i]) * p.scale;
+            if (c.edge && col > c.causal_limit) x = -INFINITY;
+            if (c.has_mask) x += add[i];
+            const float t2 = x * c.k2;
+            const float e = (i & 1) ? poly_exp2(t2) : fast_exp2(t2);      // ex2.approx: -inf -> 0, overflow -> inf -> rcp 0
+            x = fmaf(fast_rcp(1.0f + e), -2.0f * cap_l2, cap_l2);
+            if (c.edge && col >= p.Sk) x = -INFINITY;
+            s[i] = __float_as_uint(x);
+        }
+    } else {
+        // no cap: log2(e) * (scale * s + mask) on packed pairs; -inf (a causal or a masked position)
+        // survives the addition either way round
+        const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), l2e2 = pack_f32x2(LOG2E, LOG2E);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            uint64_t v = (uint64_t)s[2 * i] | ((uint64_t)s[2 * i + 1] << 32);
+            if (c.has_mask) {
+                uint64_t m2 = pack_f32x2(add[2 * i], add[2 * i + 1]);
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(m2) : "l"(m2), "l"(l2e2));
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(v) : "l"(v), "l"(sc2), "l"(m2));
+            } else {
+                asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(v) : "l"(v), "l"(sc2));
+            }
+            s[2 * i] = (uint32_t)v;
+            s[2 * i + 1] = (uint32_t)(v >> 32);
+        }
+        if (c.edge) mask_chunk(s, cbase, min(c.causal_limit, p.Sk - 1));
+    }
 }
 
 // Number of key blocks a query tile starting at row q0 needs.
@@ -397,8 +385,8 @@ __device__ __forceinline__ WorkItem decode_item(const FaParams& p, int idx) {
     return w;
 }
 
-// FORM 0: plain (scale and the causal rule only); 1: with a mask (rewritten blocks out of line); 2: with a softcap
-// (every block is rewritten, inline), with or without a mask.
+// FORM 0: plain (scale and the causal rule only); 1: with a mask (only the blocks it changes are rewritten); 2: with a
+// softcap (every block is rewritten), with or without a mask.
 template <bool BF16, int HD, int FORM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -689,41 +677,46 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const WorkItem w = decode_item(p, idx);
         const int nblk = w.nblk[t], q0 = w.q0, head = w.head, batch = w.batch;
         const int qrow = q0 + t * BQ + row_in_tile;
-        const char* mask_row = nullptr;      // this query row's mask values (rows past Sq read the last row: their output is never stored)
-        if constexpr (GENERAL) {
-            if (p.mask)
-                mask_row = (const char*)p.mask + ((int64_t)batch * p.mask_strides[0] + (int64_t)head * p.mask_strides[1] +
-                                                  (int64_t)min(qrow, p.Sq - 1) * p.mask_strides[2]) * (p.mask_bool ? 1 : 4);
-        }
+        // This query row's mask values (rows past Sq read the last row: their output is never stored).  Computed where it is
+        // needed, so that nothing of the mask stays live across the plain blocks.
+        auto mask_row_of = [&]() -> const char* {
+            if (!GENERAL || !p.mask) return nullptr;
+            return (const char*)p.mask + ((int64_t)batch * p.mask_strides[0] + (int64_t)head * p.mask_strides[1] +
+                                          (int64_t)min(qrow, p.Sq - 1) * p.mask_strides[2]) * (p.mask_bool ? 1 : 4);
+        };
+        const char* mask_row = nullptr;
         // A mask whose rows are all the same (a key-padding mask): the 32 lanes share the scan "does it change anything
         // in this block", four values each, fetched one block ahead.  A block that is not whole counts as changed.
-        const bool mask_shared = GENERAL && mask_row != nullptr && p.mask_strides[2] == 0 && p.mask_vec != 0 && p.softcap <= 0.0f;
-        auto scan_fetch = [&](int jb) {
+        bool mask_shared = false;
+        auto scan_fetch = [&](const char* row, int jb) {
             const int c = jb * BKV + 4 * lane;
             if (c + 4 > p.Sk) return p.mask_bool ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(1u, 0u, 0u, 0u);
-            if (p.mask_bool) return make_uint4(__ldg(reinterpret_cast<const unsigned int*>(mask_row + c)), 0u, 0u, 0u);
-            return __ldg(reinterpret_cast<const uint4*>(mask_row + 4 * c));
+            if (p.mask_bool) return make_uint4(__ldg(reinterpret_cast<const unsigned int*>(row + c)), 0u, 0u, 0u);
+            return __ldg(reinterpret_cast<const uint4*>(row + 4 * c));
         };
         uint4 scan_next = make_uint4(0u, 0u, 0u, 0u);
-        if (mask_shared && nblk > 0) scan_next = scan_fetch(0);
         float m_used = -INFINITY;   // maximum the stored P and O are expressed against (log2 domain)
         float l = 0.0f;
-        for (int j = 0; j < nblk && ok; ++j) {
+        // One key block of this tile.  `general` (a compile-time tag) selects the form with the per-block question and the
+        // rewrite; the plain form is the whole loop of a run without mask or softcap, and the leading blocks a key-padding
+        // mask leaves alone run through it too.  Returns false when a wait gave up.
+        auto block = [&](auto general, int j) -> bool {
+            constexpr bool G = decltype(general)::value;
             ok = mbar_wait(bar_sfull + 8 * t, (cum + j) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, j);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) return false;
             tc_fence_after();
             const int col0 = j * BKV;
             // Only the diagonal block and a ragged last block need element-wise masking.
             // General form: does this block need its scores rewritten (a softcap, or a mask that is not all "attend"
             // here)?  Blocks a mask leaves alone -- all of them but the boundary for a key-padding mask -- take the plain path.
             bool rewrite = false;
-            if constexpr (GENERAL) {
-                rewrite = p.softcap > 0.0f;
+            if constexpr (G) {
+                rewrite = FORM == 2;        // a softcap rewrites every block
                 if (!rewrite && mask_shared) {
                     // the lanes' four values each of this block were requested one block ago; request the next block's now
                     const uint4 cur = scan_next;
-                    if (j + 1 < nblk) scan_next = scan_fetch(j + 1);
+                    if (j + 1 < nblk) scan_next = scan_fetch(mask_row, j + 1);
                     const bool any = p.mask_bool ? __vcmpeq4(cur.x, 0u) != 0u : (cur.x | cur.y | cur.z | cur.w) != 0u;
                     rewrite = __any_sync(0xffffffffu, any);
                 } else if (!rewrite && mask_row) {
@@ -733,30 +726,75 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             const bool need_mask = !rewrite && ((p.causal && col0 + BKV - 1 > q0 + t * BQ + p.causal_offset) || (col0 + BKV > p.Sk));
             const int col_limit = p.causal ? min(p.Sk - 1, qrow + p.causal_offset) : p.Sk - 1;   // last visible column of this row
-            const float sc = rewrite ? 1.0f : p.scale_log2;     // a rewritten block leaves log2-domain scores in tensor memory
+            const float sc = rewrite ? 1.0f : p.scale_log2;     // a rewritten block holds log2-domain scores
 
             // One pass over the row: with the registers the rebalancing gives the softmax warps, all 128 scores stay in
             // registers from the row maximum through the exponentials -- no second read of S from tensor memory.
-            float mx_rewritten = 0.0f;
-            if (GENERAL && rewrite) {
-                // rare for a key-padding mask (its boundary blocks only), every block under a softcap
-                if constexpr (FORM == 2) mx_rewritten = rewrite_scores(p, tS, mask_row, col0, qrow, q0 + t * BQ);
-                else mx_rewritten = rewrite_scores_out_of_line(p, tS, mask_row, col0, qrow, q0 + t * BQ);
-            }
             uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_ld_32x32b_x32(tS, s0);
-            tmem_ld_32x32b_x32(tS + 32, s1);
-            tmem_ld_32x32b_x32(tS + 64, s2);
-            tmem_ld_32x32b_x32(tS + 96, s3);
-            tmem_wait_ld();
-            if (need_mask) {   // masked scores become -inf: they drop out of the max and exponentiate to 0
-                mask_chunk(s0, col0, col_limit);
-                mask_chunk(s1, col0 + 32, col_limit);
-                mask_chunk(s2, col0 + 64, col_limit);
-                mask_chunk(s3, col0 + 96, col_limit);
+            // Under a softcap the blocks above the causal diagonal are not skipped: every score there is -inf before the
+            // cap and -cap after it (the reference applies tanh last), whatever Q K^T and the mask say.
+            const bool all_capped = G && FORM == 2 && p.causal && col0 > q0 + t * BQ + BQ - 1 + p.causal_offset;
+            if (all_capped) {
+                const uint32_t capped = __float_as_uint(-p.softcap * LOG2E);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    s0[i] = col0 + i < p.Sk ? capped : 0xff800000u;
+                    s1[i] = col0 + 32 + i < p.Sk ? capped : 0xff800000u;
+                    s2[i] = col0 + 64 + i < p.Sk ? capped : 0xff800000u;
+                    s3[i] = col0 + 96 + i < p.Sk ? capped : 0xff800000u;
+                }
+            } else {
+                tmem_ld_32x32b_x32(tS, s0);
+                tmem_ld_32x32b_x32(tS + 32, s1);
+                tmem_ld_32x32b_x32(tS + 64, s2);
+                tmem_ld_32x32b_x32(tS + 96, s3);
+                if (G && (FORM == 2 || rewrite)) {
+                    // every block under a softcap; for a key-padding mask its boundary blocks only.  The row is rewritten
+                    // where it sits (registers), one chunk of mask values at a time; the first is requested before the wait.
+                    const RewriteConsts rc = rewrite_consts(p, mask_row, col0, qrow, q0 + t * BQ);
+                    float add[32];
+                    load_mask_values(p, mask_row, col0, add);
+                    tmem_wait_ld();
+                    if constexpr (FORM == 2) {
+                        // Every block is rewritten: one copy of the transform in the instruction stream, run four times.  The
+                        // chunk to rewrite is always s0 and the four chunks rotate through it (four rotations put every chunk
+                        // back where it was).  Unrolled four times the block loop outgrows the instruction cache: measured,
+                        // the warps then wait for instructions more often than for anything else.
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            if (c > 0) load_mask_values(p, mask_row, col0 + 32 * c, add);
+                            rewrite_chunk<true>(p, rc, s0, add, col0 + 32 * c);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const uint32_t first = s0[i];
+                                s0[i] = s1[i];
+                                s1[i] = s2[i];
+                                s2[i] = s3[i];
+                                s3[i] = first;
+                            }
+                        }
+                    } else {
+                        // Mask form: a rewritten block is the exception (the boundary of a key-padding mask), straight-line
+                        // code off the hot path costs the plain blocks nothing.
+                        rewrite_chunk<false>(p, rc, s0, add, col0);
+                        load_mask_values(p, mask_row, col0 + 32, add);
+                        rewrite_chunk<false>(p, rc, s1, add, col0 + 32);
+                        load_mask_values(p, mask_row, col0 + 64, add);
+                        rewrite_chunk<false>(p, rc, s2, add, col0 + 64);
+                        load_mask_values(p, mask_row, col0 + 96, add);
+                        rewrite_chunk<false>(p, rc, s3, add, col0 + 96);
+                    }
+                } else {
+                    tmem_wait_ld();
+                    if (need_mask) {   // masked scores become -inf: they drop out of the max and exponentiate to 0
+                        mask_chunk(s0, col0, col_limit);
+                        mask_chunk(s1, col0 + 32, col_limit);
+                        mask_chunk(s2, col0 + 64, col_limit);
+                        mask_chunk(s3, col0 + 96, col_limit);
+                    }
+                }
             }
-            const float mx = (GENERAL && rewrite) ? mx_rewritten
-                                                  : fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
+            const float mx = fmaxf(fmaxf(max_chunk(s0), max_chunk(s1)), fmaxf(max_chunk(s2), max_chunk(s3)));
             const float m_new = fmaxf(m_used, mx * sc);
             float alpha = 1.0f;
             bool need = false;
@@ -769,7 +807,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // O_t is only touched between "P V of block j-1 retired" and "P of block j published".
                 ok = mbar_wait(bar_pvdone + 8 * t, (cum + j - 1) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 100000 + j);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
+                if (!ok) return false;
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
@@ -803,6 +841,34 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(bar_pfull + 8 * t);
+            return true;
+        };
+        // Leading blocks that a key-padding mask leaves alone (all of them but the last one or two, usually) take the plain
+        // form: the lanes scan eight blocks at a time, four mask values each, until the first block that changes anything.
+        int j_plain = FORM == 0 ? nblk : 0;
+        if (FORM == 1 && p.mask_strides[2] == 0 && p.mask_vec != 0) {
+            const char* row = mask_row_of();
+            j_plain = nblk;
+            for (int jb = 0; jb < nblk && j_plain == nblk; jb += 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[u] = jb + u < nblk ? scan_fetch(row, jb + u) : (p.mask_bool ? make_uint4(0x01010101u, 0u, 0u, 0u) : make_uint4(0u, 0u, 0u, 0u));
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const bool any = p.mask_bool ? __vcmpeq4(v[u].x, 0u) != 0u : (v[u].x | v[u].y | v[u].z | v[u].w) != 0u;
+                    if (__any_sync(0xffffffffu, any)) j_plain = min(j_plain, jb + u);
+                }
+            }
+        }
+        for (int j = 0; j < j_plain && ok; ++j) ok = block(std::false_type{}, j);
+        if constexpr (GENERAL) {
+            if (j_plain < nblk) {
+                mask_row = mask_row_of();
+                mask_shared = FORM == 1 && mask_row != nullptr && p.mask_strides[2] == 0 && p.mask_vec != 0;
+                if (mask_shared) scan_next = scan_fetch(mask_row, j_plain);
+            }
+            for (int j = j_plain; j < nblk && ok; ++j) ok = block(std::true_type{}, j);
         }
 
         // epilogue: O / l -> global
