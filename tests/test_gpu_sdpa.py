@@ -267,6 +267,33 @@ def test_head_sharded_delivery_by_tile_stores_into_stand_in_peers(dev, D):
         x.free()
 
 
+def test_tile_store_delivery_under_back_pressure_seven_stand_in_peers(dev):
+    """Eight destinations per output tile (the local O and seven stand-ins for peers) and work items so short that
+    the tile stores, not the arithmetic, set the pace: 1024 items of at most four key blocks on 148 CTAs, 0.5 GB of
+    stores against 35 GFLOP.  Each use of the one staging tile then waits for the copy engine, with the softmax warps
+    of both query tiles queueing behind it.  All eight copies must be identical, sampled heads must match the oracle,
+    and no pipeline wait may give up."""
+    B, H, S, D = 16, 32, 512, 128
+    rng = np.random.default_rng(77)
+    q, k, v = (orc.normal_bf16(rng, (B, H, S, D)) for _ in range(3))
+    Q, K, V = dev.from_numpy(q), dev.from_numpy(k), dev.from_numpy(v)
+    outs = [dev.from_numpy(np.full((B, H, S, D), 0xFFFF, np.uint16)) for _ in range(8)]
+    for _ in range(3):        # the later launches start with the copy engine still busy
+        dev.sdpa(Q, K, V, outs[0], B, H, H, S, S, D, dtype=mk.MK_BF16, causal=True, peers=[o.ptr for o in outs[1:]])
+    dev.sync()
+    assert dev.kernel_status() == 0
+    bf = orc.bf16_to_f32
+    first = outs[0].copyout(np.uint16, (B, H, S, D))
+    assert not np.any(first == 0xFFFF), "part of the output was never written"
+    for o in outs[1:]:
+        assert np.array_equal(o.copyout(np.uint16, (B, H, S, D)), first), "the copies differ from each other"
+    for b, h in ((0, 0), (5, 17), (15, 31), (9, 2)):
+        ref = orc.sdpa_f32(bf(q[b:b + 1, h:h + 1]), bf(k[b:b + 1, h:h + 1]), bf(v[b:b + 1, h:h + 1]), causal=True)
+        assert_close(bf(first[b:b + 1, h:h + 1]), ref, mk.MK_BF16, f"batch {b} head {h}")
+    for x in [Q, K, V] + outs:
+        x.free()
+
+
 def oracle_sdpa_broadcast_mask(q, k, v, mask4, causal, softcap=0.0, scale=None):
     """The oracle takes one [Sq, Sk] mask; a mask that broadcasts over batch and head is applied pair by pair
     (bool masks become 0 / -inf first, tensor/src/transformer.rs:112-124)."""
@@ -299,6 +326,13 @@ def mask_strides(shape4, Sk):
     ("softcap only", 1, 4, 2, 256, 512, 128, None, False, False, 30.0),
     ("softcap under a causal rule: masked scores become -cap and take part", 1, 2, 2, 384, 384, 128, None, False, True, 20.0),
     ("bool mask and softcap, head size 64", 2, 2, 1, 200, 264, 64, (2, 1, 200), True, False, 15.0),
+    # long key ranges: the scan for the first block a key-padding mask changes runs several rounds of eight blocks
+    ("key padding late in a long ragged sequence", 2, 2, 2, 256, 1500, 128, (2, 1, 1), False, False, 0.0),
+    ("bool key padding, long, causal, head size 64", 2, 2, 1, 1280, 1280, 64, (2, 1, 1), True, True, 0.0),
+    ("key padding with a hole in the middle: plain blocks, a changed one, unchanged ones, the tail", 2, 2, 2, 200, 1408, 128, (2, 1, 1), False, False, 0.0),
+    ("a key-padding mask that changes nothing", 1, 2, 2, 384, 1152, 128, (1, 1, 1), False, True, 0.0),
+    ("softcap, causal, long and ragged: whole blocks above the diagonal", 1, 2, 1, 650, 650, 128, None, False, True, 25.0),
+    ("softcap and key padding, causal, long", 2, 2, 2, 640, 640, 128, (2, 1, 1), True, True, 30.0),
 ])
 def test_masks_and_softcap_run_on_the_tensor_core_kernel(dev, case):
     name, B, H, Hkv, Sq, Sk, D, mshape, is_bool, causal, cap = case
@@ -318,8 +352,12 @@ def test_masks_and_softcap_run_on_the_tensor_core_kernel(dev, case):
             mask4 = (rng.standard_normal(shape4) * 2).astype(np.float32)
             if mshape[2] == 1:
                 mask4[:] = 0
-                for b in range(shape4[0]):
-                    mask4[b, ..., Sk - 23 * (b + 1):] = -np.inf
+                if "changes nothing" not in name:
+                    for b in range(shape4[0]):
+                        mask4[b, ..., Sk - 23 * (b + 1):] = -np.inf
+                if "hole" in name:
+                    mask4[..., 300:310] = -np.inf
+                    mask4[1, ..., 700] = -1.5
     Q, K, V = (dev.from_numpy(orc.f32_to_bf16(t)) for t in (q, k, v))
     O = dev.alloc(B * H * Sq * D * 2)
     kw = {}
