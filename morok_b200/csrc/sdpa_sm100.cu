@@ -42,14 +42,18 @@ using namespace ptx;
 
 constexpr int BQ = 128;                 // query rows per tile (two tiles per CTA)
 constexpr int BKV = 128;                // keys per block
-// Per head size (D == Dv, 64 or 128).  A tile of 128 rows is HD / 64 boxes of 64 columns (16 KiB each,
-// 128-byte swizzled); with 64-wide heads the K / V ring is four stages deep in the same 128 KiB.
+// Per head size (D == Dv: 64, 128 or 256).  A tile of 128 rows is HD / 64 boxes of 64 columns (16 KiB each,
+// 128-byte swizzled); with 64-wide heads the K / V ring is four stages deep in the same 128 KiB.  256-wide heads
+// run one query tile per CTA: O alone takes 256 of the 512 tensor-memory columns, and Q, one K block and one V block
+// (64 KiB each) fill shared memory, so the K / V "rings" are a single stage -- which is enough for one tile, because
+// the next K is only needed after this block's softmax and P V, and the next V after the next S and softmax.
 template <int HD>
 struct Cfg {
     static constexpr int TILE_BYTES = BQ * HD * 2;
     static constexpr int HALF_BYTES = BQ * 64 * 2;
-    static constexpr int KV_STAGES = HD == 64 ? 4 : 2;
-    static constexpr int SMEM_Q = 2 * TILE_BYTES;
+    static constexpr int TILES = HD == 256 ? 1 : 2;                       // query tiles per CTA (see below)
+    static constexpr int KV_STAGES = HD == 64 ? 4 : (HD == 256 ? 1 : 2);
+    static constexpr int SMEM_Q = TILES * TILE_BYTES;
     static constexpr int SMEM_K = KV_STAGES * TILE_BYTES;
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
     static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 3 + 2;
@@ -92,7 +96,8 @@ struct FaParams {
     float* lse;
     int64_t o_strides[3];
     uint32_t idesc_qk, idesc_pv;
-    int q_pairs;        // ceil(Sq / 256)
+    int q_pairs;        // work items per (batch, head): ceil(Sq / (tiles * 128))
+    int tiles;          // query tiles of 128 rows per work item: 2, or 1 for 256-wide heads
     unsigned int* work_counter;   // device-wide claim counter, zeroed before the launch
     int tma_o;          // stage O in a tile of shared memory from which warp 10 issues one tile store per destination
                         // (always when peers receive copies, and for head sizes the kernel pads)
@@ -378,9 +383,9 @@ __device__ __forceinline__ WorkItem decode_item(const FaParams& p, int idx) {
     w.head = bh % p.Hq;
     w.batch = bh / p.Hq;
     w.kv_head = w.head / (p.Hq / p.Hkv);
-    w.q0 = pair * 2 * BQ;
+    w.q0 = pair * p.tiles * BQ;
     w.nblk[0] = blocks_for_tile(p, w.q0);
-    w.nblk[1] = blocks_for_tile(p, w.q0 + BQ);
+    w.nblk[1] = p.tiles == 2 ? blocks_for_tile(p, w.q0 + BQ) : 0;
     w.nmax = max(w.nblk[0], w.nblk[1]);
     return w;
 }
@@ -397,8 +402,8 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     constexpr bool GENERAL = FORM != 0;
     // P is published in two halves of 64 keys, so that the first four P V steps run while the second half is exponentiated.
     // 64-wide heads are bound by the softmax warps, not by the chain softmax -> P V -> next S: there the second barrier only costs.
-    constexpr bool P_HALVES = HD == 128;
-    constexpr int PE = HD == 128 ? 4 : 3;     // every PE-th pair of exponentials runs on the FMA pipes (measured best per head size)
+    constexpr bool P_HALVES = HD >= 128;
+    constexpr int PE = HD == 64 ? 3 : 4;     // every PE-th pair of exponentials runs on the FMA pipes (measured best per head size)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sQ = smem_u32(smem), sK = sQ + SMEM_Q, sV = sK + SMEM_K;
@@ -505,9 +510,9 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 ok = __all_sync(0xffffffffu, mbar_wait(bar_qempty, (n & 1) ^ 1, abort_flag, p.kerr, KERR_SDPA_PRODUCER_WAIT, 600000 + n));
                 if (!ok) break;
                 if (leader) {
-                    mbar_arrive_expect_tx(bar_q, 2 * TILE_BYTES);
+                    mbar_arrive_expect_tx(bar_q, Cfg<HD>::TILES * TILE_BYTES);
 #pragma unroll
-                    for (int t = 0; t < 2; ++t)
+                    for (int t = 0; t < Cfg<HD>::TILES; ++t)
 #pragma unroll
                         for (int h = 0; h < NH; ++h)
                             tma_load_4d(sQ + t * TILE_BYTES + h * HALF_BYTES, &tmQ, bar_q, h * 64, w.q0 + t * BQ, w.head, w.batch);
@@ -999,8 +1004,10 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     // Head sizes: the kernel is built for 64 and 128 columns; any head size that is a multiple of 8 (16-byte rows) up to 128
     // runs on the next larger one -- the tile loads zero-fill the columns past D (zero products in Q K^T, zero
     // columns of O) and the stores of O drop them.
-    if (d.D != d.Dv || d.D % 8 != 0 || d.D < 8 || d.D > 128) return MK_OK;
-    const int HDk = d.D <= 64 ? 64 : 128;
+    if (d.D != d.Dv || d.D % 8 != 0 || d.D < 8 || (d.D > 128 && d.D != 256)) return MK_OK;
+    const int HDk = d.D <= 64 ? 64 : (d.D <= 128 ? 128 : 256);
+    // 256-wide heads: no room for an output staging tile, so no peers and no padded head sizes there
+    if (HDk == 256 && (d.n_peers > 0 || getenv("MOROK_B200_ATTN_TMA_O") != nullptr)) return MK_OK;
     if (d.Sk <= 0 || d.Sq <= 0) return MK_OK;
     if (d.causal && d.causal_offset < 0) return MK_OK;   // rows without any visible key (NaN rows) are the general kernel's business
     if (!strides_ok(d.q_strides, d.D) || !strides_ok(d.k_strides, d.D) || !strides_ok(d.v_strides, d.D)) return MK_OK;
@@ -1010,7 +1017,8 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
         return MK_OK;
     for (int i = 0; i < d.n_peers; ++i)
         if (reinterpret_cast<uintptr_t>(d.peer_O[i]) & 15) return MK_OK;
-    const int64_t q_pairs = (d.Sq + 2 * BQ - 1) / (2 * BQ);
+    const int tiles = HDk == 256 ? 1 : 2;
+    const int64_t q_pairs = (d.Sq + tiles * BQ - 1) / (tiles * BQ);
     const int64_t items = q_pairs * d.B * d.Hq;
     if (items > 0x7fffffffll) return MK_OK;
     const int64_t grid = items < dev->prop.multiProcessorCount ? items : dev->prop.multiProcessorCount;
@@ -1052,6 +1060,7 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     p.idesc_qk = idesc_f16(fmt, 0u, 0u, BQ, BKV);
     p.idesc_pv = idesc_f16(fmt, 0u, 1u, BQ, (uint32_t)HDk);
     p.q_pairs = (int)q_pairs;
+    p.tiles = tiles;
     // Peers receive their copies as tile stores issued from a staging tile; without peers every thread stores its
     // own row (MOROK_B200_ATTN_TMA_O forces the staged form for measurements).
     // ... and for head sizes the kernel pads to 64 / 128 columns: the tile store drops the padding columns
@@ -1093,7 +1102,9 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
         else if (form == 1) MK_FA(BF, HD_, 1, SMEM);        \
         else MK_FA(BF, HD_, 0, SMEM);                       \
     } while (0)
-    if (HDk == 128) {
+    if (HDk == 256) {
+        if (bf) MK_FA_FORMS(true, 256, Cfg<256>::SMEM_BYTES); else MK_FA_FORMS(false, 256, Cfg<256>::SMEM_BYTES);
+    } else if (HDk == 128) {
         if (bf) MK_FA_FORMS(true, 128, smem128); else MK_FA_FORMS(false, 128, smem128);
     } else {
         if (bf) MK_FA_FORMS(true, 64, smem64); else MK_FA_FORMS(false, 64, smem64);
@@ -1101,7 +1112,8 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
 #undef MK_FA_FORMS
 #undef MK_FA
     MK_CUDA(cudaGetLastError());
-    note_launch(dev, st, HDk == 128 ? (general ? "sdpa_tc_d128_general" : "sdpa_tc_d128") : (general ? "sdpa_tc_d64_general" : "sdpa_tc_d64"));
+    note_launch(dev, st, HDk == 256 ? (general ? "sdpa_tc_d256_general" : "sdpa_tc_d256")
+                         : HDk == 128 ? (general ? "sdpa_tc_d128_general" : "sdpa_tc_d128") : (general ? "sdpa_tc_d64_general" : "sdpa_tc_d64"));
     *handled = true;
     return MK_OK;
 }

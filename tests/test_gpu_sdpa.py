@@ -418,3 +418,47 @@ def test_other_head_sizes_run_on_the_tensor_core_kernel(dev, case, D):
     assert not np.any(got_bits == 0xFFFF)
     assert np.all(guard.copyout(np.uint16, (4096,)) == 0xABCD)
     assert_close(orc.bf16_to_f32(got_bits), orc.sdpa_f32(q, k, v, causal=causal), mk.MK_BF16, f"D={D} {case}")
+
+
+@pytest.mark.parametrize("case", [
+    # name, B, Hq, Hkv, Sq, Sk, causal, dtype, mask?, softcap
+    ("causal, several key blocks and items", 2, 4, 2, 640, 640, True, mk.MK_BF16, False, 0.0),
+    ("ragged, no causal rule, f16", 1, 3, 3, 200, 333, False, mk.MK_F16, False, 0.0),
+    ("one query tile, many key blocks", 1, 2, 1, 100, 1500, False, mk.MK_BF16, False, 0.0),
+    ("key-padding mask, causal", 2, 2, 2, 384, 384, True, mk.MK_BF16, True, 0.0),
+    ("softcap", 1, 2, 2, 256, 384, True, mk.MK_BF16, False, 25.0),
+])
+def test_head_size_256_runs_on_the_tensor_core_kernel(dev, case):
+    """256-wide heads: one query tile per CTA (O takes half of tensor memory), single-stage K / V.  The reference is
+    generic in the head size (tensor/src/transformer.rs:88-96); LSE checked as well."""
+    name, B, H, Hkv, Sq, Sk, causal, dt, masked, cap = case
+    D = 256
+    rng = np.random.default_rng(Sq + Sk)
+    rnd = orc.round_bf16 if dt == mk.MK_BF16 else (lambda x: x.astype(np.float16).astype(np.float32))
+    q, k, v = (rnd(rng.standard_normal(s, dtype=np.float32)) for s in ((B, H, Sq, D), (B, Hkv, Sk, D), (B, Hkv, Sk, D)))
+    to_dev = (lambda t: dev.from_numpy(orc.f32_to_bf16(t))) if dt == mk.MK_BF16 else (lambda t: dev.from_numpy(t.astype(np.float16)))
+    Q, K, V = (to_dev(t) for t in (q, k, v))
+    O = dev.from_numpy(np.full((B, H, Sq, D), 0xFFFF, np.uint16))
+    L = dev.alloc(B * H * Sq * 4)
+    kw = {}
+    mask4 = None
+    if masked:
+        mask4 = np.zeros((B, 1, 1, Sk), np.float32)
+        for b in range(B):
+            mask4[b, ..., Sk - 37 * (b + 1):] = -np.inf
+        kw = dict(mask=dev.from_numpy(mask4), mask_strides=mask_strides(mask4.shape, Sk))
+    dev.profile_begin()
+    dev.sdpa(Q, K, V, O, B, H, Hkv, Sq, Sk, D, dtype=dt, causal=causal, softcap=cap, lse=L, **kw)
+    launched = [n for n, _ in dev.profile_end()]
+    assert launched == ["sdpa_tc_d256_general" if (masked or cap > 0) else "sdpa_tc_d256"], launched
+    assert dev.kernel_status() == 0
+    bits = O.copyout(np.uint16, (B, H, Sq, D))
+    assert not np.any(bits == 0xFFFF)
+    got = orc.bf16_to_f32(bits) if dt == mk.MK_BF16 else bits.view(np.float16).astype(np.float32)
+    if mask4 is not None:
+        ref = oracle_sdpa_broadcast_mask(q, k, v, mask4, causal, cap)
+    else:
+        ref, lse_ref = orc.sdpa_f32(q, k, v, causal=causal, softcap=cap, return_lse=True)
+        lse = L.copyout(np.float32, (B, H, Sq))
+        assert np.allclose(lse, lse_ref, rtol=2e-3, atol=2e-3), name
+    assert_close(got, ref, dt, name)
