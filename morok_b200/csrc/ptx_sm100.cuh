@@ -93,6 +93,40 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Bounded wait until a counter in shared memory, which only ever grows, has reached `target`.  For hand-offs whose
+// waiters may fall more than one step behind the signaller: an mbarrier wait sees only the parity of a phase, a counter
+// cannot be mistaken.  The signaller stores with release semantics (st_release_shared_u32), the waiter loads with acquire.
+__device__ __forceinline__ void st_release_shared_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_shared_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool counter_wait_ge(uint32_t addr, uint32_t target, volatile uint32_t* abort_flag, KernelError* kerr,
+                                                unsigned int code, unsigned int detail, uint64_t limit_ns = kWaitLimitNs) {
+    if (ld_acquire_shared_u32(addr) >= target) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (ld_acquire_shared_u32(addr) >= target) return true;
+        __nanosleep(32);
+        if ((++spins & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > limit_ns) {
+                *abort_flag = 1u;
+                if (atomicCAS(&kerr->code, 0u, code) == 0u) {
+                    kerr->block = blockIdx.x;
+                    kerr->detail = detail;
+                }
+                __threadfence();
+                return false;
+            }
+        }
+    }
+}
+
 // ---- TMA -------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

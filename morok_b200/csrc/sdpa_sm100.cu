@@ -56,7 +56,7 @@ struct Cfg {
     static constexpr int SMEM_Q = TILES * TILE_BYTES;
     static constexpr int SMEM_K = KV_STAGES * TILE_BYTES;
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 3 + 2;
+    static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 1 + 2;
     static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + 1024 + 512;      // + alignment slack + barriers and slots
     // head-sharded runs that deliver O by tile stores stage one 128-row tile of output beside the operands
     static constexpr int SMEM_BYTES_DELIVER = SMEM_BYTES + TILE_BYTES;
@@ -424,13 +424,13 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const uint32_t bar_ifull = bar_ofree + 16;               // [2] work-item slot published by the producer
     const uint32_t bar_iempty = bar_ifull + 16;              // [2] work-item slot read by every consumer
     const uint32_t bar_ostage_full = bar_iempty + 16;        // output staging tile written by the four warps of a query tile
-    // [2] ... and read out by the tile stores warp 10 issued: use u of the staging tile completes a phase of barrier u & 1.
-    // Two barriers because a softmax warp may come to wait for use u while use u - 2 is still being read out (the other
-    // tile has not even staged use u - 1): on a single barrier that waiter would be two phases ahead, and a parity wait
-    // cannot tell "two phases ahead" from "done".  With one barrier per parity of u every waiter is at most one phase ahead
-    // of its barrier, because the same warp waited for use u - 3 or a later one before it staged its previous tile.
-    const uint32_t bar_ostage_free = bar_ostage_full + 8;
-    const uint32_t bar_phalf = bar_ostage_free + 16;         // [2] first 64 keys of P_t written (only when P is published in halves)
+    const uint32_t bar_phalf = bar_ostage_full + 8;          // [2] first 64 keys of P_t written (only when P is published in halves)
+    // "The staging tile is free again" is a counter, not a barrier: the number of uses the tile stores of warp 10 have
+    // read out.  The warps of a query tile wait until it has reached their use number.  A barrier would not do: its
+    // waits see the parity of a phase only, and a waiter here can be two or more uses behind -- a tile that sat out an
+    // item or two (a last, half-filled pair of tiles), or one that comes to wait while the copy engine is still busy with
+    // the use before the other tile's -- and would take an old phase for its own.
+    const uint32_t stage_freed = smem_u32(tmem_slot + 4);
     volatile int* item_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2] claimed item indices
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -440,8 +440,6 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         mbar_init(bar_q, 1);
         mbar_init(bar_qempty, 1);     // Q tiles are free once the item's last S MMA retired (one commit)
         mbar_init(bar_ostage_full, 128);
-        mbar_init(bar_ostage_free, 1);
-        mbar_init(bar_ostage_free + 8, 1);
         for (int i = 0; i < KV_STAGES; ++i) {
             mbar_init(bar_kfull + 8 * i, 1);
             mbar_init(bar_kempty + 8 * i, 1);
@@ -458,6 +456,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_init(bar_iempty + 8 * t, 1 + 8 + (p.tma_o ? 1 : 0));    // MMA warp, eight softmax warps, and the store warp when it takes part
         }
         *abort_flag = 0;
+        tmem_slot[4] = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmQ);
         prefetch_tensormap(&tmK);
@@ -654,7 +653,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                         for (int d = 0; d <= p.n_peers; ++d) tma_store_4d(&omaps.m[d], src + h * HALF_BYTES, h * 64, w.q0 + t * BQ, w.head, w.batch);
                     bulk_commit_group();
                     bulk_wait_group_read<0>();
-                    mbar_arrive(bar_ostage_free + 8 * (u & 1));
+                    st_release_shared_u32(stage_freed, u + 1);
                 }
                 __syncwarp();
                 ++u;
@@ -897,7 +896,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 // while these warps move on to their next item.  The staging tile serves both query tiles in turn:
                 // use u = uses of earlier items + (tile 1 after a tile 0 that had work).
                 const uint32_t u = stage_uses + ((t == 1 && w.nblk[0] > 0) ? 1u : 0u);
-                if (u > 0) ok = mbar_wait(bar_ostage_free + 8 * ((u - 1) & 1), ((u - 1) >> 1) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 900000 + n);
+                ok = counter_wait_ge(stage_freed, u, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 900000 + n);
                 ok = __all_sync(0xffffffffu, ok);
                 if (ok) {
     #pragma unroll 1

@@ -267,13 +267,15 @@ def test_head_sharded_delivery_by_tile_stores_into_stand_in_peers(dev, D):
         x.free()
 
 
-def test_tile_store_delivery_under_back_pressure_seven_stand_in_peers(dev):
+@pytest.mark.parametrize("S", [512, 384])
+def test_tile_store_delivery_under_back_pressure_seven_stand_in_peers(dev, S):
     """Eight destinations per output tile (the local O and seven stand-ins for peers) and work items so short that
     the tile stores, not the arithmetic, set the pace: 1024 items of at most four key blocks on 148 CTAs, 0.5 GB of
     stores against 35 GFLOP.  Each use of the one staging tile then waits for the copy engine, with the softmax warps
     of both query tiles queueing behind it.  All eight copies must be identical, sampled heads must match the oracle,
-    and no pipeline wait may give up."""
-    B, H, S, D = 16, 32, 512, 128
+    and no pipeline wait may give up.  S = 384: every second item has rows for one query tile only, so the other
+    tile's warps sit items out and come back several uses of the staging tile later."""
+    B, H, D = 16, 32, 128
     rng = np.random.default_rng(77)
     q, k, v = (orc.normal_bf16(rng, (B, H, S, D)) for _ in range(3))
     Q, K, V = dev.from_numpy(q), dev.from_numpy(k), dev.from_numpy(v)
