@@ -1006,7 +1006,7 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     if (d.D != d.Dv || d.D % 8 != 0 || d.D < 8 || (d.D > 128 && d.D != 256)) return MK_OK;
     const int HDk = d.D <= 64 ? 64 : (d.D <= 128 ? 128 : 256);
     // 256-wide heads: no room for an output staging tile, so no peers and no padded head sizes there
-    if (HDk == 256 && (d.n_peers > 0 || getenv("MOROK_B200_ATTN_TMA_O") != nullptr)) return MK_OK;
+    if (HDk == 256 && d.n_peers > 0) return MK_OK;
     if (d.Sk <= 0 || d.Sq <= 0) return MK_OK;
     if (d.causal && d.causal_offset < 0) return MK_OK;   // rows without any visible key (NaN rows) are the general kernel's business
     if (!strides_ok(d.q_strides, d.D) || !strides_ok(d.k_strides, d.D) || !strides_ok(d.v_strides, d.D)) return MK_OK;
@@ -1063,7 +1063,16 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     // Peers receive their copies as tile stores issued from a staging tile; without peers every thread stores its
     // own row (MOROK_B200_ATTN_TMA_O forces the staged form for measurements).
     // ... and for head sizes the kernel pads to 64 / 128 columns: the tile store drops the padding columns
-    p.tma_o = d.n_peers > 0 || d.D != HDk || getenv("MOROK_B200_ATTN_TMA_O") != nullptr;
+    // ... and for 128-wide heads with long key ranges, where a work item lasts long enough for the one staging tile not
+    // to be contended: the staged tile leaves through the copy engine in 128-byte rows, while row-per-thread stores
+    // cost the softmax warps ~3000 cycles per tile (measured: +1.5 % causal and +2 % non-causal at S = 4096, +1 % at
+    // 8192; -2 % at S = 2048 and -11 % at 1024, -2 % for 64-wide heads -- hence the rule).  MOROK_B200_ATTN_TMA_O=1 / 0
+    // forces the staged / the direct form where both are possible.
+    p.tma_o = d.n_peers > 0 || d.D != HDk || (HDk == 128 && d.Sk >= 4096);
+    if (const char* e = getenv("MOROK_B200_ATTN_TMA_O")) {
+        if (atoi(e) != 0 && HDk != 256) p.tma_o = 1;
+        else if (d.n_peers == 0 && d.D == HDk) p.tma_o = 0;
+    }
     alignas(64) OStoreMaps omaps{};
     if (p.tma_o) {
         for (int i = 0; i <= d.n_peers; ++i) {
