@@ -564,3 +564,30 @@ def test_sharded_delivery_by_tile_stores_into_stand_in_peers(dev):
         assert np.array_equal(c, first), "the copies differ from each other"
     for x in [A, B] + outs:
         x.free()
+
+
+def test_tile_store_delivery_under_back_pressure_seven_stand_in_peers(dev):
+    """Eight destinations per tile and a K so short that the tile stores set the pace (0.27 GB of stores against
+    4 GFLOP): every epilogue warp queues behind the copy engine for its staging blocks, launch after launch.  All
+    eight copies must be identical and match the oracle; no pipeline wait may give up."""
+    M, K, N = 4096, 128, 4096
+    rng = np.random.default_rng(33)
+    a, b = orc.normal_bf16(rng, (M, K), 1.0), orc.normal_bf16(rng, (K, N), 0.05)
+    A, B = dev.from_numpy(a), dev.from_numpy(b)
+    outs = [dev.from_numpy(np.full((M, N), 0xFFFF, np.uint16)) for _ in range(8)]
+    dev.profile_begin()
+    for _ in range(3):
+        dev.gemm(A, B, outs[0], M, N, K, mk.MK_BF16, peers=[o.ptr for o in outs[1:]])
+    launched = [name for name, _ in dev.profile_end()]
+    assert launched == ["gemm_tc_pair_deliver"] * 3, launched
+    dev.sync()
+    assert dev.kernel_status() == 0
+    first = outs[0].copyout(np.uint16, (M, N))
+    assert not np.any(first == 0xFFFF)
+    rows = np.r_[0:64, 2000:2064, M - 64:M]
+    assert_close(orc.bf16_to_f32(first[rows]), orc.matmul_f32(orc.bf16_to_f32(a[rows]), orc.bf16_to_f32(b)), mk.MK_BF16, "sampled rows")
+    for o in outs[1:]:
+        assert np.array_equal(o.copyout(np.uint16, (M, N)), first), "the copies differ from each other"
+    for x in [A, B] + outs:
+        x.free()
+
