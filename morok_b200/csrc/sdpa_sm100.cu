@@ -741,19 +741,7 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // One pass over the row: with the registers the rebalancing gives the softmax warps, all 128 scores stay in
             // registers from the row maximum through the exponentials -- no second read of S from tensor memory.
             uint32_t s0[32], s1[32], s2[32], s3[32];
-            // Under a softcap the blocks above the causal diagonal are not skipped: every score there is -inf before the
-            // cap and -cap after it (the reference applies tanh last), whatever Q K^T and the mask say.
-            const bool all_capped = G && FORM == 2 && p.causal && col0 > q0 + t * BQ + BQ - 1 + p.causal_offset;
-            if (all_capped) {
-                const uint32_t capped = __float_as_uint(-p.softcap * LOG2E);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    s0[i] = col0 + i < p.Sk ? capped : 0xff800000u;
-                    s1[i] = col0 + 32 + i < p.Sk ? capped : 0xff800000u;
-                    s2[i] = col0 + 64 + i < p.Sk ? capped : 0xff800000u;
-                    s3[i] = col0 + 96 + i < p.Sk ? capped : 0xff800000u;
-                }
-            } else {
+            {
                 tmem_ld_32x32b_x32(tS, s0);
                 tmem_ld_32x32b_x32(tS + 32, s1);
                 tmem_ld_32x32b_x32(tS + 64, s2);
@@ -853,6 +841,59 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             mbar_arrive(bar_pfull + 8 * t);
             return true;
         };
+        // Under a softcap the blocks above the causal diagonal are not skipped: every score there is -inf before the cap
+        // and -cap after it (the reference applies tanh last), whatever Q K^T and the mask say.  Such a block needs no
+        // read of S and one exponential per row: P is the same value in all 128 columns.
+        auto capped_block = [&](int j) -> bool {
+            ok = mbar_wait(bar_sfull + 8 * t, (cum + j) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, j);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return false;
+            tc_fence_after();
+            const float capped = -p.softcap * LOG2E;
+            const float m_new = fmaxf(m_used, capped);
+            float alpha = 1.0f;
+            bool need = false;
+            if (m_new > m_used + RESCALE_THRESHOLD) {
+                alpha = fast_exp2(m_used - m_new);
+                m_used = m_new;
+                need = true;
+            }
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+                ok = mbar_wait(bar_pvdone + 8 * t, (cum + j - 1) & 1, abort_flag, p.kerr, KERR_SDPA_SOFTMAX_WAIT, 100000 + j);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) return false;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(tO + c * 32, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                    tmem_st_32x32b_x32(tO + c * 32, r);
+                }
+            }
+            const float e = fast_exp2(capped - m_used);
+            l = l * alpha + float(BKV) * e;
+            uint32_t pe;
+            if constexpr (BF16) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(e, e);
+                pe = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+                __half2 h = __floats2half2_rn(e, e);
+                pe = *reinterpret_cast<uint32_t*>(&h);
+            }
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pk[i] = pe;
+            tmem_st_32x32b_x32(tS, pk);
+            tmem_st_32x32b_x32(tS + 32, pk);
+            tmem_wait_st();
+            tc_fence_before();
+            if constexpr (P_HALVES) mbar_arrive(bar_phalf + 8 * t);
+            mbar_arrive(bar_pfull + 8 * t);
+            return true;
+        };
         // Leading blocks that a key-padding mask leaves alone (all of them but the last one or two, usually) take the plain
         // form: the lanes scan eight blocks at a time, four mask values each, until the first block that changes anything.
         int j_plain = FORM == 0 ? nblk : 0;
@@ -878,7 +919,11 @@ sdpa_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 mask_shared = FORM == 1 && mask_row != nullptr && p.mask_strides[2] == 0 && p.mask_vec != 0;
                 if (mask_shared) scan_next = scan_fetch(mask_row, j_plain);
             }
-            for (int j = j_plain; j < nblk && ok; ++j) ok = block(std::true_type{}, j);
+            // first key block that lies entirely above the causal diagonal of this tile and is whole (softcap form only)
+            int j_capped = nblk;
+            if (FORM == 2 && p.causal) j_capped = min(nblk, max(0, (q0 + t * BQ + BQ - 1 + p.causal_offset) / BKV + 1));
+            for (int j = j_plain; j < nblk && ok; ++j)
+                ok = (j >= j_capped && (j + 1) * BKV <= p.Sk) ? capped_block(j) : block(std::true_type{}, j);
         }
 
         // epilogue: O / l -> global
