@@ -1,20 +1,21 @@
 // Fused attention forward on Blackwell tensor cores (sm_100a): head sizes up to 128 (built for 64 and 128 columns;
-// other multiples of 8 run zero-padded on the next larger one).
+// other multiples of 8 run zero-padded on the next larger one) and 256.
 //
 // One kernel replaces the >= 5 kernels (and the materialised [Sq,Sk] score matrix) that morok
 // schedules for `scaled_dot_product_attention` (tensor/src/transformer.rs:78-137):
 // O = softmax(causal(Q K^T * scale)) V with an online softmax whose running maximum and sum stay
 // in f32 registers.
 //
-// A CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong:
+// A CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong (one tile for 256-wide heads).
+// Twelve warps = three warpgroups; the control warpgroup gives registers to the two softmax warpgroups (setmaxnreg):
 //
-//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one thread per query row; first the row maximum of
-//                    its 128 scores in tensor memory, then the scores again 32 columns at a time:
-//                    exp2 (three pairs in four on the special-function unit, the fourth as a
-//                    polynomial on the FMA pipes), P (16 bit) written back over S, m and l in
-//                    registers; O is rescaled only when the maximum moved by > 2^8; finally O is
-//                    normalised and stored -- 128-bit stores of each thread's row, or, when peer GPUs
-//                    receive copies (head-sharded runs) or the head size is padded, into a staging tile
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one thread per query row.  The row's 128 scores of a key block
+//                    are read from tensor memory once and stay in registers: row maximum, exp2 (three pairs in
+//                    four on the special-function unit, the fourth as a polynomial on the FMA pipes), P (16 bit)
+//                    written back over S -- for 128-wide heads published in two halves of 64 keys; m and l in
+//                    registers; O is rescaled only when the maximum moved by > 2^8; finally O is normalised and
+//                    stored -- 128-bit stores of each thread's row, or into a staging tile that leaves by tile
+//                    stores (peer GPUs receive copies, padded head sizes, long key ranges)
 //   warp 8           TMA producer: claims work items, Q per item, then K / V blocks of 128 keys
 //                    through a ring that runs on across items
 //   warp 9           MMA issuer: S_t = Q_t K^T and O_t += P_t V, tile 0 and tile 1 interleaved so the
@@ -24,11 +25,12 @@
 //   warp 10          tensor-memory allocation (512 columns: S0 S1 at 0 / 128, O0 O1 at 256 / 384); then, for
 //                    staged output, one tile store per destination (local O and every peer's O over
 //                    NVLink) of each staged tile
+//   warp 11          idle (register rebalancing works per warpgroup of four warps)
 //
 // K is a K-major B operand, V an MN-major one (read as stored, no transpose), P is the A operand
 // taken from tensor memory.  Key blocks entirely above the causal diagonal are never loaded.
 // A mask (additive or bool, any shape that broadcasts against the scores) and a softcap run in the same
-// kernel: its general form rewrites the scores in tensor memory during the row-maximum pass.
+// kernel: its general form rewrites the scores of a block where they sit, in the softmax warps' registers.
 // All barrier waits are bounded; a wait that gives up records a code in the device error word.
 #include <cstdlib>
 #include <type_traits>
@@ -58,8 +60,7 @@ struct Cfg {
     static constexpr int SMEM_V = KV_STAGES * TILE_BYTES;
     static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6 + 1 + 2 + 4 + 1 + 2;
     static constexpr int SMEM_BYTES = SMEM_Q + SMEM_K + SMEM_V + 1024 + 512;      // + alignment slack + barriers and slots
-    // head-sharded runs that deliver O by tile stores stage one 128-row tile of output beside the operands
-    static constexpr int SMEM_BYTES_DELIVER = SMEM_BYTES + TILE_BYTES;
+    // (runs whose output leaves by tile stores add one 128-row staging tile beside the operands: the launcher asks for it)
 };
 // Tensor maps of the output as every destination sees it: [0] the local O, [1 ..] the peers' O
 // ([B, H, S, D] with the caller's strides; box of 64 columns x 128 rows, 128-byte swizzle).
@@ -1147,7 +1148,7 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
         return cudaSuccess;
     };
     const bool bf = d.dtype == MK_BF16;
-    const int smem128 = p.tma_o ? Cfg<128>::SMEM_BYTES_DELIVER : Cfg<128>::SMEM_BYTES, smem64 = p.tma_o ? Cfg<64>::SMEM_BYTES_DELIVER : Cfg<64>::SMEM_BYTES;
+    const int smem128 = Cfg<128>::SMEM_BYTES + (p.tma_o ? Cfg<128>::TILE_BYTES : 0), smem64 = Cfg<64>::SMEM_BYTES + (p.tma_o ? Cfg<64>::TILE_BYTES : 0);
 #define MK_FA(BF, HD_, FORM_, SMEM) MK_CUDA(launch(sdpa_tc_kernel<BF, HD_, FORM_>, SMEM))
 #define MK_FA_FORMS(BF, HD_, SMEM)                          \
     do {                                                    \
