@@ -13,7 +13,10 @@
 //   warps 4-7 epilogue     : tcgen05.ld -> alpha, + beta D (matrix or bias row), or the SwiGLU gate of a
 //                            pair of products -> cast -> shared-memory staging -> 128-bit global
 //                            stores in whole 256-byte row segments, to the local C and, for
-//                            N-sharded runs, straight into every peer GPU's C
+//                            N-sharded runs, straight into every peer GPU's C.  The CTA-pair form delivers
+//                            sharded 16-bit outputs differently: the epilogue warps write 32 x 64 blocks in
+//                            tile-store layout and one lane issues a tile store per destination, so the copy
+//                            engine moves the bytes while the next accumulator is drained
 // For M > 128 the CTA-pair form below is used (two CTAs share each MMA, 256 x 256 tiles); for M <= 128
 // and long K the tile's K range is cut into units so that every SM streams weights (see gemm_sm100()).
 //
