@@ -1121,8 +1121,13 @@ mk_status sdpa_sm100(mk_device* dev, cudaStream_t st, const mk_sdpa_desc& d, flo
     }
     alignas(64) OStoreMaps omaps{};
     if (p.tma_o) {
+        const bool optional = d.n_peers == 0 && d.D == HDk;     // the staged form is a choice here, not a need
         for (int i = 0; i <= d.n_peers; ++i) {
             s1 = encode_bhsd(&omaps.m[i], d.dtype, i == 0 ? d.O : d.peer_O[i - 1], d.B, d.Hq, d.Sq, d.Dv, d.o_strides);
+            if (s1 != MK_OK && optional) {       // an output layout the tile store cannot describe: direct stores take any
+                p.tma_o = 0;
+                break;
+            }
             if (s1 != MK_OK) return s1;
         }
     }

@@ -87,9 +87,12 @@ def test_tensor_core_head_sizes_vs_oracle(dev, case, dt, D):
         assert_close(o[:, :, 0], np.repeat(v, H // Hkv, axis=1)[:, :, 0], dt, "row 0 == V[0]")
 
 
-def test_strided_bshd_layout(dev):
-    """Q/K/V stored [B,S,H,D] (the projection output layout) are read in place through strides."""
-    B, S, H, Hkv, D = 2, 256, 4, 2, 128
+@pytest.mark.parametrize("S", [256, 4096])
+def test_strided_bshd_layout(dev, S):
+    """Q/K/V stored [B,S,H,D] (the projection output layout) are read in place through strides, and O is written in that
+    layout too -- by each thread's own stores for the short sequence, through the staging tile and tile stores for the
+    long one."""
+    B, H, Hkv, D = (2, 4, 2, 128) if S == 256 else (1, 2, 1, 128)
     rng = np.random.default_rng(1)
     q = orc.round_bf16(rng.standard_normal((B, S, H, D), dtype=np.float32))
     k = orc.round_bf16(rng.standard_normal((B, S, Hkv, D), dtype=np.float32))
