@@ -162,6 +162,12 @@ def test_argument_validation_reports_messages():
     with pytest.raises(mk.MorokError) as e:
         dev.sdpa(a, a, a, a, 1, 3, 2, 2, 2, 2, dtype=mk.MK_F32)   # Hq not a multiple of Hkv
     assert "multiple" in str(e.value)
+    with pytest.raises(mk.MorokError) as e:                        # a mask that broadcasts is described by strides >= 0
+        dev.sdpa(a, a, a, a, 1, 2, 2, 2, 2, 8, dtype=mk.MK_BF16, mask=a, mask_strides=(-4, 0, 2))
+    assert e.value.status == _ffi.MK_ERR_INVALID and "mask stride" in str(e.value)
+    with pytest.raises(mk.MorokError) as e:                        # every announced peer needs a buffer
+        dev.sdpa(a, a, a, a, 1, 2, 2, 2, 2, 8, dtype=mk.MK_BF16, peers=[0])
+    assert e.value.status == _ffi.MK_ERR_INVALID and "peer_O" in str(e.value)
     dev.close()
 
 
